@@ -10,7 +10,10 @@ sequence.
   A page holds PAGE = 64 consecutive positions of one sequence.
 * A group with a window gives a page back as soon as all its positions lie before every
   window that a later token can have, so in steady state it holds about ``window`` positions
-  per sequence.
+  per sequence.  Pages that hold any of a sequence's first ``keep_first`` positions are never given back
+  before the sequence ends.
+* ``needs`` may be longer than the schedule: what follows the schedule's entries is state that belongs to
+  the model and not to a layer (the token before a sequence's next one, for an embedding that reads pairs).
 * State: ``state [entry with state, slot, elems]`` (float32 unless the mixer asks otherwise), zeroed when a slot is taken.
 * Values may have another head size and another number of heads than keys (``KVNeed.v_head_dim``, ``v_heads``): the
   pools are then shaped accordingly (this library's attention kernels take equal shapes; a mixer that asks for
@@ -94,8 +97,8 @@ class Cache:
                 g.v = torch.zeros((len(g.entries), self.n_pages + 1, v_heads, PAGE, v_dim), dtype=dtype, device=self.device)
             for e in self.state_entries:
                 kind = needs[e].state_dtype
-                if kind not in ("float32", "bfloat16", "engine"):
-                    raise ValueError(f"schedule entry {e}: state_dtype must be float32, bfloat16 or engine, not {kind!r}")
+                if kind not in ("float32", "bfloat16", "int32", "engine"):
+                    raise ValueError(f"schedule entry {e}: state_dtype must be float32, bfloat16, int32 or engine, not {kind!r}")
                 sd = dtype if kind == "engine" else getattr(torch, kind)
                 self.state[e] = torch.zeros(max_seqs + 1, needs[e].state_elems, dtype=sd, device=self.device)
 
@@ -153,7 +156,7 @@ class Cache:
                 continue
             oldest = first_needed - g.need.window + 1
             row = g.table[slot]
-            for pi in range(len(row)):
+            for pi in range(pages_for(g.need.keep_first), len(row)):
                 if (pi + 1) * PAGE - 1 >= oldest:
                     break
                 if row[pi] >= 0:

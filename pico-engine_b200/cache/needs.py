@@ -7,7 +7,8 @@ from typing import Optional
 
 @dataclass(frozen=True)
 class KVNeed:
-    """Keys and values of every position (``window`` None) or of the last ``window`` positions.
+    """Keys and values of every position (``window`` None) or of the last ``window`` positions and, with ``keep_first`` = f,
+    of a sequence's first f positions as well.
     ``v_head_dim``: the size of a value head where it is not the keys' (None: the same); ``v_heads``: the
     number of value heads where it is not the keys' (a cache that keeps one compressed row per position
     asks for one key head and no value head: ``v_heads=0``)."""
@@ -16,6 +17,7 @@ class KVNeed:
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
     v_heads: Optional[int] = None
+    keep_first: int = 0
 
     @property
     def value_shape(self):
@@ -27,7 +29,7 @@ class KVNeed:
 @dataclass(frozen=True)
 class CacheNeeds:
     """``kv``: paged keys and values, or None.  ``state_elems``: numbers of fixed-size state per sequence
-    (0 for none), kept as ``state_dtype`` ("float32", "bfloat16", or "engine" for the engine's own dtype);
+    (0 for none), kept as ``state_dtype`` ("float32", "bfloat16", "int32", or "engine" for the engine's own dtype);
     the state is zero when a sequence starts."""
     kv: Optional[KVNeed] = None
     state_elems: int = 0

@@ -167,7 +167,11 @@ class GatedAttentionSpec(PartSpec):
     mixer's own input before the output projection: o <- o * sigmoid(W_g h) (``gate`` None: no gate).  ``position``
     acts on queries and keys; with ``qk_unit_norm`` every query and key head is then divided by its root mean square
     (eps ``norm_eps``, no weight).  Keys and values may have different head sizes; ``window`` as in
-    :class:`GQAAttentionSpec`.  No biases.  Tensor names are ``prefix + name``."""
+    :class:`GQAAttentionSpec`, and with ``keep_first`` = f the first f keys of a sequence stay visible behind the window
+    (key j is seen from i iff j <= i and (i - j < window or j < f)).  ``distance_slopes`` (one number a head, or None):
+    slope_h * (i - j) is taken off the score of query i and key j before the softmax.  ``bias``: the four projections
+    have bias vectors (``name + bias_suffix``).  ``own_kv`` False: the mixer has no key and value projections and reads
+    the keys and values another schedule entry wrote (``ScheduleEntry.cache_of``).  Tensor names are ``prefix + name``."""
     hidden: int
     n_heads: int
     n_kv_heads: int
@@ -183,6 +187,68 @@ class GatedAttentionSpec(PartSpec):
     q_name: str = "q"
     k_name: str = "k"
     v_name: str = "v"
+    o_name: str = "o"
+    keep_first: int = 0
+    distance_slopes: Optional[Tuple[float, ...]] = None
+    bias: bool = False
+    bias_suffix: str = ".b"
+    own_kv: bool = True
+    cache_span: Optional[Tuple[Optional[int], int]] = None   # (window, keep_first) the cache keeps where other entries that read it see further; None: this mixer's own
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec(PartSpec):
+    """Softmax attention whose keys and values are projections of one low-rank row per position.  q = W_q h, laid out head
+    by head as [``head_dim`` plain | ``rot_dim`` rotated] entries.  W_dkv h has ``kv_rank`` + ``rot_dim`` entries: the first
+    ``kv_rank``, RMS-normed (eps ``norm_eps``, plain weight ``dkv_norm``), are the latent row c; the others are one rotated key
+    part that all heads share.  Head h's plain key is W_uk,h c and its value W_uv,h c; score = (q_plain . k_plain + q_rot . k_rot)
+    * ``scale``; every earlier key is visible.  ``position`` (a :class:`RotaryPairsSpec` over ``rot_dim`` entries) turns q_rot and
+    k_rot.  Head h's output is multiplied by sigmoid((W_g h)_h), one number a head (``gate`` None: no gate), then W_o.
+    The cache keeps c and the rotated key part, nothing else.  Tensor names are ``prefix + name``."""
+    hidden: int
+    n_heads: int
+    head_dim: int
+    rot_dim: int
+    v_head_dim: int
+    kv_rank: int
+    scale: float
+    position: PartSpec
+    prefix: str
+    norm_eps: float = 1e-6
+    gate: Optional[str] = "g"
+    q_name: str = "q"
+    dkv_name: str = "dkv"
+    dkv_norm: str = "dkv.norm"
+    uk_name: str = "uk"
+    uv_name: str = "uv"
+    o_name: str = "o"
+
+
+@dataclass(frozen=True)
+class StateSpaceSpec(PartSpec):
+    """A selective state-space mixer with a scalar decay a head.  W_in h = [z | x | B | C | dt] with z, x of ``n_heads`` *
+    ``head_dim``, B and C of ``n_groups`` * ``state`` and dt of ``n_heads`` entries.  x, B and C pass a causal convolution
+    of ``taps`` taps a channel (weight [channels, taps], the last column the current token's, bias ``conv_name + bias_suffix``)
+    and silu.  dt <- softplus(dt + dt_bias).  Head h (group h // (n_heads / n_groups)):
+    S_t = exp(-exp(A_log_h) dt) S_(t-1) + dt B_t x_t^T  (S [state, head_dim] float32, zero at a sequence's start),
+    y_t = S_t^T C_t + D_h x_t.  y * silu(z) is RMS-normed in ``norm_groups`` equal runs (eps ``norm_eps``) times ``norm_name``,
+    then W_o.  The state and the last ``taps`` - 1 inputs of the convolution are kept per sequence."""
+    hidden: int
+    n_heads: int
+    head_dim: int
+    state: int
+    n_groups: int
+    taps: int
+    norm_groups: int
+    prefix: str
+    norm_eps: float = 1e-6
+    in_name: str = "in"
+    conv_name: str = "conv"
+    bias_suffix: str = ".b"
+    dt_bias_name: str = "dt_bias"
+    a_log_name: str = "A_log"
+    d_name: str = "D"
+    norm_name: str = "norm"
     o_name: str = "o"
 
 
@@ -273,7 +339,10 @@ class MixtureSpec(PartSpec):
     """``n_experts`` gated feed-forwards (``prefix + expert_name.format(e) + "." + gate/up/down``) of which a token uses
     the ``top_k`` with the largest router logits (``prefix + router_name`` [n_experts, hidden], float32), weighted by the
     softmax over the chosen logits alone.  ``shared_intermediate`` not None: one more expert (``prefix + shared_name``)
-    runs for every token and is added, multiplied by sigmoid(w_sg . h) (``shared_gate_name`` [1, hidden])."""
+    runs for every token and is added, multiplied by sigmoid(w_sg . h) (``shared_gate_name`` [1, hidden]; None: added as it is).
+    ``gated`` False: an expert is down(act(up(x))) and has no gate matrix (``activation`` then also takes "relu2").
+    ``scores`` "softmax_all": the weights are the chosen experts' entries of the softmax over all experts, not renormalised
+    ("softmax_chosen": the softmax over the chosen logits alone); either way they are multiplied by ``route_scale``."""
     hidden: int
     n_experts: int
     top_k: int
@@ -284,7 +353,10 @@ class MixtureSpec(PartSpec):
     router_name: str = "router"
     expert_name: str = "e{}"
     shared_name: str = "shared"
-    shared_gate_name: str = "shared.sg"
+    shared_gate_name: Optional[str] = "shared.sg"
+    gated: bool = True
+    scores: str = "softmax_chosen"
+    route_scale: float = 1.0
     gate_name: str = "gate"
     up_name: str = "up"
     down_name: str = "down"
@@ -298,7 +370,9 @@ class LayerSpec:
 
     ``arrangement`` names an entry of ``parts.registry.ARRANGEMENTS``; "pre_norm" is
     x += mixer(norm(x)); x += ffn(norm(x))  (pico-engine src/pico_engine/model.py:167-237); "parallel" is
-    x += mixer(norm1(x)) + ffn(norm2(x)), both halves reading the same x.
+    x += mixer(norm1(x)) + ffn(norm2(x)), both halves reading the same x; "post_norm" is
+    x += scale1 * norm1(mixer(x)); x += scale2 * norm2(ffn(x)): the sublayers read the stream as it is and the norms
+    act on their outputs (``mixer_scale`` / ``feed_forward_scale`` name the scale vectors; None: no scale).
     Every part is optional: a block without a feed-forward is a mixer-only block (pico-engine's
     recurrent layers are such, src/pico_engine/model.py:389-406), one without a mixer a feed-forward-only
     block, and a half without a norm takes the residual stream as it is.
@@ -311,6 +385,19 @@ class LayerSpec:
     mixer_input: Optional[PartSpec] = None           # applied to norm(x) before the mixer reads it (a CausalConvAddSpec)
     feed_forward_input: Optional[PartSpec] = None    # the same for the feed-forward
     residual_scale: float = 1.0                      # x += residual_scale * sublayer(norm(x))
+    mixer_scale: Optional[str] = None                # "post_norm": tensor [hidden] the normed output of the mixer is multiplied by
+    feed_forward_scale: Optional[str] = None         # the same for the feed-forward
+
+
+@dataclass(frozen=True)
+class BigramTableSpec(PartSpec):
+    """Added to the embedded token: row (previous * mul_prev + current * mul_cur) mod buckets of ``table`` [buckets + 1,
+    hidden]; a sequence's first token takes row ``buckets``.  The previous token is kept per sequence."""
+    hidden: int
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+    table: str = "bigram"
 
 
 @dataclass(frozen=True)
@@ -339,6 +426,7 @@ class ModelPlan:
     embedding_position: Optional[PartSpec] = None    # added to the embedding by position (a SinusoidAddSpec); None: nothing
     logit_softcap: Optional[float] = None            # logits <- cap * tanh(logits / cap); None: logits as projected
     stream_vectors: Tuple[Tuple[str, int], ...] = ()  # (tensor name, rows): [rows, hidden] tensors whose rows schedule entries add to the stream
+    embedding_pairs: Optional[PartSpec] = None       # added to the embedding by (previous token, token) (a BigramTableSpec); None: nothing
 
     def validate(self) -> None:
         if not self.layers:

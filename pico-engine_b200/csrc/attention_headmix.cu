@@ -32,6 +32,8 @@ struct HeadMixArgs {
     const void* sink; int sink_dtype;
     const void* mix; int mix_dtype;
     int QT, splits;
+    const float* slopes; int keep_first; int v_ld;   // slope_h * (i - j) is taken off a score (null: nothing); the first keep_first keys stay
+                                                     // visible behind the window; a value row has v_ld entries of which the first Dv are read
     float* stats;                             // [tile][split][QT][H][2]
     float* opart;                             // [tile][split][QT][H][Dv]
     void* out;                                // [T][H * Dv]
@@ -72,10 +74,14 @@ __global__ void __launch_bounds__(HM_THREADS) headmix_kernel(HeadMixArgs a) {
     if (!hm_tile(a, blockIdx.x, ti)) return;
     const int split = blockIdx.y, tid = threadIdx.x;
     const int hi = ti.p0 + ti.nq;                        // one past the last visible key
-    const int lo = (a.window > 0 && ti.p0 - a.window + 1 > 0) ? (ti.p0 - a.window + 1) & ~(HM_KB - 1) : 0;
-    int span = (hi - lo + a.splits - 1) / a.splits;
-    span = (span + HM_KB - 1) & ~(HM_KB - 1);
-    const int k_begin = lo + split * span, k_end = min(hi, k_begin + span);
+    int lo = (a.window > 0 && ti.p0 - a.window + 1 > 0) ? (ti.p0 - a.window + 1) & ~(HM_KB - 1) : 0;
+    // the kept first keys are blocks of their own in front of the window's, unless the window reaches them anyway
+    int kept_blocks = (a.window > 0 && a.keep_first > 0) ? (a.keep_first + HM_KB - 1) / HM_KB : 0;
+    if (lo <= kept_blocks * HM_KB) { lo = 0; kept_blocks = 0; }
+    const int n_blocks = kept_blocks + (hi - lo + HM_KB - 1) / HM_KB;
+    const int per_split = (n_blocks + a.splits - 1) / a.splits;
+    const int b_begin = split * per_split, b_end = min(n_blocks, b_begin + per_split);
+    const int k_end = hi;
     const int* table = a.table + (size_t)ti.row * a.table_stride;
     const T* qg = (const T*)a.q;
     const T* kp = (const T*)a.k_pool;
@@ -109,7 +115,8 @@ __global__ void __launch_bounds__(HM_THREADS) headmix_kernel(HeadMixArgs a) {
     for (int r = 0; r < NACC; ++r) acc[r] = 0.f;
     __syncthreads();
 
-    for (int kb = k_begin; kb < k_end; kb += HM_KB) {
+    for (int blk = b_begin; blk < b_end; ++blk) {
+        const int kb = blk < kept_blocks ? blk * HM_KB : lo + (blk - kept_blocks) * HM_KB;
         const int page = table[kb / PE_PAGE];
         const int in_page = kb % PE_PAGE;
         // keys of the block, all key/value heads
@@ -124,7 +131,8 @@ __global__ void __launch_bounds__(HM_THREADS) headmix_kernel(HeadMixArgs a) {
         for (int e = tid; e < H * QT * HM_KB; e += HM_THREADS) {
             const int j = e % HM_KB, i = (e / HM_KB) % QT, h = e / (HM_KB * QT);
             const int key = kb + j, qpos = ti.p0 + i;
-            const bool seen = page >= 0 && i < ti.nq && key < k_end && key <= qpos && (a.window <= 0 || qpos - key < a.window);
+            const bool seen = page >= 0 && i < ti.nq && key < k_end && key <= qpos &&
+                              (a.window <= 0 || qpos - key < a.window || key < a.keep_first);
             float s = -INFINITY;
             if (seen) {
                 const float* qv = q_s + ((size_t)i * H + h) * D;
@@ -132,6 +140,7 @@ __global__ void __launch_bounds__(HM_THREADS) headmix_kernel(HeadMixArgs a) {
                 float dot = 0.f;
                 for (int d = 0; d < D; ++d) dot = fmaf(qv[d], kv[d], dot);
                 s = dot * a.scale;
+                if (a.slopes) s -= a.slopes[h] * (float)(qpos - key);
             }
             if (PASS == 0) p_s[e] = s;
             else p_s[e] = seen ? expf(s - m_s[i * H + h]) * l_s[i * H + h] : 0.f;
@@ -159,7 +168,7 @@ __global__ void __launch_bounds__(HM_THREADS) headmix_kernel(HeadMixArgs a) {
         for (int e = tid; e < G * HM_KB * Dv; e += HM_THREADS) {
             const int d = e % Dv, j = (e / Dv) % HM_KB, c = e / (Dv * HM_KB);
             float v = 0.f;
-            if (page >= 0 && kb + j < k_end) v = to_f(vp[(((size_t)page * G + c) * PE_PAGE + in_page + j) * Dv + d]);
+            if (page >= 0 && kb + j < k_end) v = to_f(vp[(((size_t)page * G + c) * PE_PAGE + in_page + j) * a.v_ld + d]);
             kv_s[((size_t)c * HM_KB + j) * pitch + d] = v;
         }
         const float* wsrc = p_s;
@@ -266,8 +275,10 @@ extern "C" int pe_attention_headmix(const void* q, int q_stride, void* out, cons
                                     const int* table, int table_stride, const int* tok_pos, const int* tok_row,
                                     const int* tiles, int n_runs, int tile_tokens, int T, int H, int G, int D, int Dv,
                                     int window, float scale, const void* sink, int sink_dtype, const void* mix, int mix_dtype,
-                                    int QT, int splits, float* scratch, void* stream) {
+                                    int QT, int splits, float* scratch, const float* slopes, int keep_first, int v_ld, void* stream) {
     if (T <= 0) return 0;
+    if (v_ld <= 0) v_ld = Dv;
+    if (v_ld < Dv || keep_first < 0) return PE_ERR_UNSUPPORTED;
     if (H <= 0 || G <= 0 || H % G || QT < 1 || splits < 1 || splits > 65535 || (tiles && (tile_tokens % QT || n_runs <= 0)))
         return PE_ERR_UNSUPPORTED;
     if ((size_t)H * QT * Dv > (size_t)64 * HM_THREADS) return PE_ERR_UNSUPPORTED;
@@ -275,7 +286,7 @@ extern "C" int pe_attention_headmix(const void* q, int q_stride, void* out, cons
     if (smem > 227 * 1024) return PE_ERR_UNSUPPORTED;
     const int n_tiles = tiles ? n_runs * (tile_tokens / QT) : T;
     HeadMixArgs a = {q, q_stride, k_pool, v_pool, table, table_stride, tok_pos, tok_row, tiles, tile_tokens, H, G, D, Dv, window,
-                     scale, sink, sink_dtype, mix, mix_dtype, QT, splits, scratch,
+                     scale, sink, sink_dtype, mix, mix_dtype, QT, splits, slopes, keep_first, v_ld, scratch,
                      scratch + (size_t)n_tiles * splits * QT * H * 2, out};
     cudaStream_t s = (cudaStream_t)stream;
     const int nacc = (int)(((size_t)H * QT * Dv + HM_THREADS - 1) / HM_THREADS);

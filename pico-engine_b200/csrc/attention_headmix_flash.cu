@@ -31,6 +31,8 @@ struct FlashMixArgs {
     const int* tiles;                         // prompt: runs of at most 64 tokens (row, first token, tokens, first position); null: single tokens
     int H, G, D, Dv, window; float scale;
     int splits, cg, ngroups;                  // ranges of keys; value heads a block; groups of value heads
+    const float* slopes; int keep_first; int v_ld;   // slope_h * (i - j) is taken off a score (null: nothing); the first keep_first keys stay
+                                                     // visible behind the window; a value row has v_ld entries of which the first Dv are read
     float* pm; float* pl; float* po;          // [T][splits][H], [T][splits][H], [T][splits][H][G][Dv]
 };
 
@@ -105,10 +107,15 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
     const int c_lo = grp * a.cg, c_n = min(a.cg, G - c_lo);   // this block's value heads
     const int nvt = Dv / 8, nv = c_n * nvt, dk = D / 16;
     const int hi = p_last + 1;
-    const int lo = (a.window > 0 && p_first - a.window + 1 > 0) ? (p_first - a.window + 1) & ~(PE_PAGE - 1) : 0;
-    int span = (hi - lo + a.splits - 1) / a.splits;
-    span = (span + PE_PAGE - 1) & ~(PE_PAGE - 1);
-    const int k_begin = lo + split * span, k_end = min(hi, k_begin + span);
+    int lo = (a.window > 0 && p_first - a.window + 1 > 0) ? (p_first - a.window + 1) & ~(PE_PAGE - 1) : 0;
+    // the pages of the kept first keys are visited in front of the window's, unless the window reaches them anyway
+    int kept_pages = (a.window > 0 && a.keep_first > 0) ? (a.keep_first + PE_PAGE - 1) / PE_PAGE : 0;
+    if (lo <= kept_pages * PE_PAGE) { lo = 0; kept_pages = 0; }
+    const int n_pages = kept_pages + (hi - lo + PE_PAGE - 1) / PE_PAGE;
+    const int per_split = (n_pages + a.splits - 1) / a.splits;
+    const int b_begin = split * per_split, b_end = min(n_pages, b_begin + per_split);
+    const int k_end = hi;
+    auto page_start = [&](int blk) { return blk < kept_pages ? blk * PE_PAGE : lo + (blk - kept_pages) * PE_PAGE; };
     const int* table = a.table + (size_t)seq * a.table_stride;
 
     // the queries of this warp's rows as A fragments
@@ -126,6 +133,11 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
     for (int n = 0; n < NVM; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     const float sl2 = a.scale * 1.4426950408889634f;          // scores in units of log2 e
+    float slope2[2] = {0.f, 0.f};                             // the rows' distance slopes in the same units
+    if (a.slopes) {
+#pragma unroll
+        for (int x = 0; x < 2; ++x) slope2[x] = live[x] ? a.slopes[head[x]] * 1.4426950408889634f : 0.f;
+    }
     const int q_first = prompt ? a.tiles[4 * blockIdx.x + 3] + warp * 16 : p_first;      // the earliest position among this warp's rows
     const bool warp_live = prompt ? (warp * 16 < a.tiles[4 * blockIdx.x + 2]) : (warp * 16 < per_kv);
 
@@ -146,9 +158,9 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
             r += k_dr; c += k_dc;
             if (c >= per) { c -= per; ++r; }
         }
-        const bf16* vsrc = a.v_pool + (((size_t)max(page, 0) * G + c_lo) * PE_PAGE) * Dv;
+        const bf16* vsrc = a.v_pool + (((size_t)max(page, 0) * G + c_lo) * PE_PAGE) * a.v_ld;
         for (int r = v_r0, c = v_c0; r < c_n * PE_PAGE;) {
-            fx_cp16(vs + (size_t)r * vp + c * 8, vsrc + (size_t)r * Dv + c * 8, (r & (PE_PAGE - 1)) < valid ? 16 : 0);
+            fx_cp16(vs + (size_t)r * vp + c * 8, vsrc + (size_t)r * a.v_ld + c * 8, (r & (PE_PAGE - 1)) < valid ? 16 : 0);
             r += v_dr; c += v_dc;
             if (c >= perv) { c -= perv; ++r; }
         }
@@ -158,12 +170,13 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
     __shared__ int v_off[32];
     if (tid < 32) v_off[tid] = tid < nv ? (tid / nvt) * PE_PAGE * vp + (tid % nvt) * 8 : 0;
     __syncthreads();
-    if (k_begin < k_end) copy_page(k_begin, 0);
+    if (b_begin < b_end) copy_page(page_start(b_begin), 0);
     int stage = 0;
 #pragma unroll 1
-    for (int kb = k_begin; kb < k_end; kb += PE_PAGE, stage ^= 1) {
+    for (int blk = b_begin; blk < b_end; ++blk, stage ^= 1) {
+        const int kb = page_start(blk);
         const int valid = table[kb / PE_PAGE] >= 0 ? min(PE_PAGE, k_end - kb) : 0;
-        if (kb + PE_PAGE < k_end) { copy_page(kb + PE_PAGE, stage ^ 1); fx_wait<1>(); }
+        if (blk + 1 < b_end) { copy_page(page_start(blk + 1), stage ^ 1); fx_wait<1>(); }
         else fx_wait<0>();
         __syncthreads();                                      // this page's copies of all threads have landed
         const bf16* k_s = stages + stage * stage_elems;
@@ -187,7 +200,7 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
         }
         // scale (into units of log2 e, so that the exponentials are single ex2 instructions), mask, the rows' new maxima
         float mx[2] = {-INFINITY, -INFINITY};
-        if (valid == PE_PAGE && a.window <= 0 && kb + PE_PAGE - 1 <= q_first) {
+        if (valid == PE_PAGE && a.window <= 0 && !a.slopes && kb + PE_PAGE - 1 <= q_first) {
             // every key of the page is seen by every row of this warp: nothing to mask
 #pragma unroll
             for (int n = 0; n < 8; ++n) {
@@ -200,8 +213,9 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
 #pragma unroll
                 for (int x = 0; x < 4; ++x) {
                     const int rr = x >> 1, j = n * 8 + (lane & 3) * 2 + (x & 1), key = kb + j;
-                    const bool seen = live[rr] && j < valid && key <= qpos[rr] && (a.window <= 0 || qpos[rr] - key < a.window);
-                    s[n][x] = seen ? s[n][x] * sl2 : -INFINITY;
+                    const bool seen = live[rr] && j < valid && key <= qpos[rr] &&
+                                      (a.window <= 0 || qpos[rr] - key < a.window || key < a.keep_first);
+                    s[n][x] = seen ? s[n][x] * sl2 - slope2[rr] * (float)(qpos[rr] - key) : -INFINITY;
                     mx[rr] = fmaxf(mx[rr], s[n][x]);
                 }
             }
@@ -360,8 +374,11 @@ static int fx_launch(const FlashMixArgs& a, dim3 grid, size_t smem, cudaStream_t
 extern "C" int pe_attention_flashmix(const void* q, int q_stride, void* out, const void* k_pool, const void* v_pool,
                                      const int* table, int table_stride, const int* tok_pos, const int* tok_row,
                                      const int* tiles, int n_runs, int T, int H, int G, int D, int Dv, int window, float scale,
-                                     const float* sink, const float* mix, int splits, float* scratch, void* stream) {
+                                     const float* sink, const float* mix, int splits, float* scratch, const float* slopes,
+                                     int keep_first, int v_ld, void* stream) {
     if (T <= 0) return 0;
+    if (v_ld <= 0) v_ld = Dv;
+    if (v_ld < Dv || v_ld % 8 || keep_first < 0) return PE_ERR_UNSUPPORTED;
     const int cg = pe_attention_flashmix_group(H, G, D, Dv);
     if (cg == 0 || splits < 1 || splits > 65535 || (tiles && n_runs <= 0)) return PE_ERR_UNSUPPORTED;
     if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15 || (q_stride & 1)) return PE_ERR_UNSUPPORTED;
@@ -370,7 +387,7 @@ extern "C" int pe_attention_flashmix(const void* q, int q_stride, void* out, con
     float* pl = pm + (size_t)T * splits * H;
     float* po = pl + (size_t)T * splits * H;
     FlashMixArgs a = {(const bf16*)q, q_stride, (const bf16*)k_pool, (const bf16*)v_pool, table, table_stride, tok_pos, tok_row, tiles,
-                      H, G, D, Dv, window, scale, splits, cg, ngroups, pm, pl, po};
+                      H, G, D, Dv, window, scale, splits, cg, ngroups, slopes, keep_first, v_ld, pm, pl, po};
     const size_t smem = 2 * 2 * ((size_t)PE_PAGE * (D + FX_PAD) + (size_t)cg * PE_PAGE * (Dv + FX_PAD));      // two stages of bfloat16
     const int merge_threads = Dv >= 256 ? Dv : (256 / Dv) * Dv;                    // whole groups of Dv threads
     const size_t merge_smem = sizeof(float) * (2 * (size_t)H * splits + 2 * (size_t)H + (size_t)merge_threads);

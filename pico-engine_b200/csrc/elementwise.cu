@@ -35,6 +35,49 @@ extern "C" int pe_embed(const void* table, int table_dtype, const int* ids, floa
     return 0;
 }
 
+// The same with a row of a second table added that the pair (previous token, token) chooses: row
+// (previous * mul_prev + token * mul_cur) mod buckets, and row `buckets` for a sequence's first token.  The token before a row's
+// first token of this step is the sequence's state (prev[slot * prev_stride]); the block of a row's first token reads it and then
+// leaves the row's last token there for the next step (no other block touches that place).
+template <typename TW>
+__global__ void embed_pairs_kernel(const TW* table, const TW* pairs, const int* ids, const int* tok_pos, const int* tok_row,
+                                   const int* row_first, const int* slots, int* prev, long long prev_stride, float* out, int H, int V,
+                                   int buckets, int mul_prev, int mul_cur) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    const int b = tok_row[t], first = row_first[b];
+    int* state = prev + (size_t)slots[b] * prev_stride;
+    int r = buckets;
+    if (tok_pos[t] > 0) {
+        const long long before = t == first ? *state : ids[t - 1];
+        r = (int)((before * mul_prev + (long long)id * mul_cur) % buckets);
+    }
+    const TW* row = table + (size_t)id * H;
+    const TW* add = pairs + (size_t)r * H;
+    float* o = out + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f(row[i]) + to_f(add[i]);
+    if (t == first) {
+        __syncthreads();                                   // every thread has read the state
+        if (threadIdx.x == 0) *state = ids[row_first[b + 1] - 1];
+    }
+}
+
+extern "C" int pe_embed_pairs(const void* table, const void* pairs, int table_dtype, const int* ids, const int* tok_pos, const int* tok_row,
+                              const int* row_first, const int* slots, int* prev, long long prev_stride, float* out, int T, int H, int V,
+                              int buckets, int mul_prev, int mul_cur, void* stream) {
+    if (T <= 0) return 0;
+    if (buckets <= 0) return PE_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (table_dtype == PE_F32) PE_TRY(pe_launch(embed_pairs_kernel<float>, T, 256, 0, s, (const float*)table, (const float*)pairs, ids, tok_pos, tok_row, row_first, slots, prev, prev_stride, out, H, V, buckets, mul_prev, mul_cur));
+    else if (table_dtype == PE_BF16) PE_TRY(pe_launch(embed_pairs_kernel<bf16>, T, 256, 0, s, (const bf16*)table, (const bf16*)pairs, ids, tok_pos, tok_row, row_first, slots, prev, prev_stride, out, H, V, buckets, mul_prev, mul_cur));
+    else return PE_ERR_UNSUPPORTED;
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
 // Token ids of a step that follows a step still in flight: ids[j] = prev[src[j]] where src[j] >= 0
 // (the token that row src[j] of the step before chose, which the host has not seen yet);
 // other ids stay as the host gave them.

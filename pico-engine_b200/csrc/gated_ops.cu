@@ -10,9 +10,9 @@ __device__ __forceinline__ float go_sigmoid(float v) { return 1.0f / (1.0f + exp
 __device__ __forceinline__ float go_gelu_tanh(float v) {
     return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
 }
-// activations: 0 none, 1 sigmoid, 2 silu, 3 gelu (tanh form)
+// activations: 0 none, 1 sigmoid, 2 silu, 3 gelu (tanh form), 4 the square of relu
 __device__ __forceinline__ float go_act(float v, int act) {
-    return act == 1 ? go_sigmoid(v) : act == 2 ? v * go_sigmoid(v) : act == 3 ? go_gelu_tanh(v) : v;
+    return act == 1 ? go_sigmoid(v) : act == 2 ? v * go_sigmoid(v) : act == 3 ? go_gelu_tanh(v) : act == 4 ? (v > 0.f ? v * v : 0.f) : v;
 }
 
 // ---------------------------------------------------------------- rotation of pairs, unit norm, cache write
@@ -524,14 +524,44 @@ extern "C" int pe_gated_act(const void* gu, void* out, int dtype, int T, int I, 
     return 0;
 }
 
+// ---------------------------------------------------------------- activation of ungated experts, a weight per group of columns
+// h [T, I]; out[t, c] = act(h[t, c]) * colw[t, min(c / group, n_groups - 1)], formed in float32 (a zero weight gives an exact zero).
+template <typename T>
+__global__ void weighted_act_kernel(const T* h, T* out, int I, int act, const float* colw, int group, int n_groups, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I, c = idx % I;
+        const float w = colw[t * n_groups + min((int)(c / group), n_groups - 1)];
+        out[idx] = from_f<T>(w == 0.f ? 0.f : go_act(to_f(h[idx]), act) * w);
+    }
+}
+
+extern "C" int pe_weighted_act(const void* h, void* out, int dtype, int T, int I, int act, const float* colw, int group, int n_groups,
+                               void* stream) {
+    if (T <= 0 || I <= 0) return 0;
+    if (!colw || group <= 0 || n_groups <= 0) return PE_ERR_UNSUPPORTED;
+    const size_t total = (size_t)T * I;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == PE_F32) PE_TRY(pe_launch(weighted_act_kernel<float>, blocks, 256, 0, s, (const float*)h, (float*)out, I, act, colw, group, n_groups, total));
+    else if (dtype == PE_BF16) PE_TRY(pe_launch(weighted_act_kernel<bf16>, blocks, 256, 0, s, (const bf16*)h, (bf16*)out, I, act, colw, group, n_groups, total));
+    else return PE_ERR_UNSUPPORTED;
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
 // ---------------------------------------------------------------- the choice of experts
 // logits [T, ld] float32: columns 0 .. E-1 are the router's, column E (extra != 0) the logit of a gate for a part that
 // every token uses.  weights [T, E + extra] float32: the softmax over the `top` largest logits at their places, zero at
 // the others (of equal logits the lower index is taken first); the extra column holds sigmoid(logit).  ids [T, top] int32
 // (or null) receives the chosen experts, largest logit first.  A warp a token.
-__device__ __forceinline__ void moe_choose(const float* z, int E, int top, int extra, float* w, int* ids, int lane) {
+// `over_all` != 0: the weights are the chosen experts' entries of the softmax over all E logits (not renormalised);
+// either way they are multiplied by `factor`.  extra == 2: there is no logit for the extra column, which holds 1.
+__device__ __forceinline__ void moe_choose(const float* z, int E, int top, int extra, float* w, int* ids, int lane,
+                                           int over_all = 0, float factor = 1.0f) {
     for (int e = lane; e < E; e += 32) w[e] = 0.f;
-    if (extra && lane == 0) w[E] = go_sigmoid(z[E]);
+    if (extra && lane == 0) w[E] = extra == 2 ? 1.0f : go_sigmoid(z[E]);
     __syncwarp();
     float zmax = 0.f, sum = 0.f;
     unsigned long long taken_lo = 0ull;                 // the lane's taken places (a lane sees E / 32 <= 64 of them)
@@ -557,28 +587,35 @@ __device__ __forceinline__ void moe_choose(const float* z, int E, int top, int e
         if (lane == 0) { w[at] = p; if (ids) ids[k] = at; }
     }
     __syncwarp();
-    const float inv = 1.0f / sum;
+    if (over_all) {                                     // the denominator runs over every expert (zmax is the largest logit of all)
+        float all = 0.f;
+        for (int e = lane; e < E; e += 32) all += expf(z[e] - zmax);
+        sum = warp_sum(all);
+    }
+    const float inv = factor / sum;
     for (int e = lane; e < E; e += 32) w[e] *= inv;
 }
 
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* logits, int ld, int E, int top, int extra, float* weights,
-                                                        int* ids, int T) {
+                                                        int* ids, int T, int over_all, float factor) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= T) return;
-    moe_choose(logits + (size_t)t * ld, E, top, extra, weights + (size_t)t * (E + extra), ids ? ids + (size_t)t * top : nullptr, lane);
+    moe_choose(logits + (size_t)t * ld, E, top, extra, weights + (size_t)t * (E + (extra ? 1 : 0)), ids ? ids + (size_t)t * top : nullptr,
+               lane, over_all, factor);
 }
 
 // The same from the float32 residual stream: the logits are router[e] . (x * rsqrt(mean(x^2) + eps) * norm_w), formed in float32
 // by the token's block (the RMS norm in front of the router is part of this kernel), for up to MR_MAX_E experts (+ the extra row).
+// norm_w null: the router reads the stream as it is (no norm).
 #define MR_MAX_E 256
 #define MR_THREADS 128
 // A block a token: its four warps share the row (each a quarter of the 16-byte units, so four times the reads are in flight),
 // their partial sums meet in shared memory in a fixed order, and the first warp chooses.
 __global__ void __launch_bounds__(MR_THREADS) moe_route_stream_kernel(const float* x, const void* norm_w, int nw_dtype, float eps,
                                                                       const float* router, int K, int E, int top, int extra,
-                                                                      float* weights, int* ids, int T) {
+                                                                      float* weights, int* ids, int T, int over_all, float factor) {
     pdl_launch_dependents();
     __shared__ float z[MR_MAX_E + 1];
     __shared__ float part[MR_THREADS / 32][8];
@@ -587,19 +624,20 @@ __global__ void __launch_bounds__(MR_THREADS) moe_route_stream_kernel(const floa
     const int t = blockIdx.x;
     pdl_wait();
     const float* row = x + (size_t)t * K;
-    const int n = E + extra;
+    const int n = E + (extra == 1 ? 1 : 0);
     // VEC (K a multiple of 4, a float32 norm weight, aligned rows): 16-byte reads, four of a thread's reads of the row in flight
     // at once for the sum of squares.
-    const bool vec = K % 4 == 0 && nw_dtype == PE_F32 && !(((uintptr_t)x | (uintptr_t)router | (uintptr_t)norm_w) & 15);
+    const bool vec = norm_w && K % 4 == 0 && nw_dtype == PE_F32 && !(((uintptr_t)x | (uintptr_t)router | (uintptr_t)norm_w) & 15);
     float ss = 0.f;
-    if (vec) {
+    if (!norm_w) {
+    } else if (vec) {
         const float4* row4 = reinterpret_cast<const float4*>(row);
 #pragma unroll 4
         for (int k = tid; k < K / 4; k += MR_THREADS) { const float4 v = row4[k]; ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
     } else {
         for (int k = tid; k < K; k += MR_THREADS) ss = fmaf(row[k], row[k], ss);
     }
-    const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)K + eps);
+    const float rstd = norm_w ? 1.0f / sqrtf(block_sum(ss, red) / (float)K + eps) : 1.0f;
     for (int e0 = 0; e0 < n; e0 += 8) {                                     // eight logits at a time: the row is read once for them
         float acc[8];
 #pragma unroll
@@ -622,7 +660,7 @@ __global__ void __launch_bounds__(MR_THREADS) moe_route_stream_kernel(const floa
             }
         } else {
             for (int k = tid; k < K; k += MR_THREADS) {
-                const float xv = row[k] * load_as_f(norm_w, nw_dtype, k);
+                const float xv = norm_w ? row[k] * load_as_f(norm_w, nw_dtype, k) : row[k];
 #pragma unroll
                 for (int u = 0; u < 8; ++u)
                     if (e0 + u < n) acc[u] = fmaf(xv, router[(size_t)(e0 + u) * K + k], acc[u]);
@@ -638,23 +676,26 @@ __global__ void __launch_bounds__(MR_THREADS) moe_route_stream_kernel(const floa
         if (tid < 8 && e0 + tid < n) z[e0 + tid] = ((part[0][tid] + part[1][tid]) + (part[2][tid] + part[3][tid])) * rstd;
     }
     __syncthreads();
-    if (warp == 0) moe_choose(z, E, top, extra, weights + (size_t)t * (E + extra), ids ? ids + (size_t)t * top : nullptr, lane);
+    if (warp == 0) moe_choose(z, E, top, extra, weights + (size_t)t * (E + (extra ? 1 : 0)), ids ? ids + (size_t)t * top : nullptr, lane,
+                              over_all, factor);
 }
 
 extern "C" int pe_moe_route_stream(const float* x, const void* norm_w, int nw_dtype, float eps, const float* router, int K, int E,
-                                   int top, int extra, float* weights, int* ids, int T, void* stream) {
+                                   int top, int extra, float* weights, int* ids, int T, int over_all, float factor, void* stream) {
     if (T <= 0) return 0;
-    if (E <= 0 || E > MR_MAX_E || top <= 0 || top > E || K <= 0) return PE_ERR_UNSUPPORTED;
+    if (E <= 0 || E > MR_MAX_E || top <= 0 || top > E || K <= 0 || extra < 0 || extra > 2) return PE_ERR_UNSUPPORTED;
     PE_TRY(pe_launch(moe_route_stream_kernel, T, MR_THREADS, 0, (cudaStream_t)stream, x, norm_w, nw_dtype, eps, router, K, E, top, extra,
-                     weights, ids, T));
+                     weights, ids, T, over_all, factor));
     PE_LAUNCH_CHECK();
     return 0;
 }
 
-extern "C" int pe_moe_route(const float* logits, int ld, int E, int top, int extra, float* weights, int* ids, int T, void* stream) {
+extern "C" int pe_moe_route(const float* logits, int ld, int E, int top, int extra, float* weights, int* ids, int T, int over_all,
+                            float factor, void* stream) {
     if (T <= 0) return 0;
-    if (E <= 0 || E > 2048 || top <= 0 || top > E) return PE_ERR_UNSUPPORTED;
-    PE_TRY(pe_launch(moe_route_kernel, (T + 3) / 4, 128, 0, (cudaStream_t)stream, logits, ld, E, top, extra, weights, ids, T));
+    if (E <= 0 || E > 2048 || top <= 0 || top > E || extra < 0 || extra > 2) return PE_ERR_UNSUPPORTED;
+    PE_TRY(pe_launch(moe_route_kernel, (T + 3) / 4, 128, 0, (cudaStream_t)stream, logits, ld, E, top, extra, weights, ids, T, over_all,
+                     factor));
     PE_LAUNCH_CHECK();
     return 0;
 }

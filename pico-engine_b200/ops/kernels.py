@@ -831,13 +831,27 @@ def headmix_mma_key_block(n_heads: int, n_kv: int, head_dim: int, v_head_dim: in
 def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, head_dim: int, v_head_dim: int,
                       k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, table_stride: int,
                       tok_pos: torch.Tensor, tok_row: torch.Tensor, window: Optional[int], scale: float,
-                      sink: Optional[torch.Tensor], mix: Optional[torch.Tensor], ctx) -> torch.Tensor:
+                      sink: Optional[torch.Tensor], mix: Optional[torch.Tensor], ctx, slopes: Optional[torch.Tensor] = None,
+                      keep_first: int = 0, values_in_keys: bool = False) -> torch.Tensor:
     """Attention of the step's tokens over the cache with the softmax weights mixed across heads (``mix`` [H, H]; None: not
-    mixed) and a sink logit a head in the denominator (``sink`` [H]; None: none); [T, H * Dv] in q's dtype."""
+    mixed) and a sink logit a head in the denominator (``sink`` [H]; None: none); [T, H * Dv] in q's dtype.  ``slopes``
+    float32 [H]: slope_h * (i - j) is taken off the score of query i and key j.  ``keep_first``: with a window, the first so many
+    keys of a sequence stay visible.  ``values_in_keys``: a position's value is the first Dv entries of its key row
+    (``v_pool`` is not read)."""
     T = tok_pos.shape[0]
-    _need(q, "q"); _need(k_pool, "k_pool", q.dtype); _need(v_pool, "v_pool", q.dtype)
-    if tuple(k_pool.shape[1:]) != (n_kv, PAGE, head_dim) or tuple(v_pool.shape[1:]) != (n_kv, PAGE, v_head_dim):
+    _need(q, "q"); _need(k_pool, "k_pool", q.dtype)
+    if values_in_keys:
+        if v_head_dim > head_dim:
+            raise KernelError("values that are part of the key rows cannot be longer than those")
+        v_pool, v_ld = k_pool, head_dim
+    else:
+        _need(v_pool, "v_pool", q.dtype)
+        v_ld = v_head_dim
+    if tuple(k_pool.shape[1:]) != (n_kv, PAGE, head_dim) or tuple(v_pool.shape[1:]) != (n_kv, PAGE, v_ld):
         raise KernelError("cache pools do not have the heads and head sizes of this attention")
+    if slopes is not None:
+        _need(slopes, "slopes", torch.float32, (n_heads,))
+    plain_mask = slopes is None and not keep_first and not values_in_keys
     if sink is not None:
         _need(sink, "sink", None, (n_heads,))
     if mix is not None:
@@ -854,7 +868,7 @@ def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, h
     floats = all(t is None or t.dtype == torch.float32 for t in (sink, mix))
     if q.dtype == torch.bfloat16 and HEADMIX_TENSOR_CORES == "1" and floats:
         cg = lib.pe_attention_flashmix_group(n_heads, n_kv, head_dim, v_head_dim)
-        if cg and q_stride % 2 == 0:
+        if cg and q_stride % 2 == 0 and v_ld % 8 == 0:
             # one pass over the keys with an output for every (head, value head), then merge + sink + mixing
             blocks = (n_runs * n_heads if tiles is not None else T * n_kv) * ((n_kv + cg - 1) // cg)
             # Few blocks (single tokens with long contexts): the keys are cut into ranges until about one and a half blocks
@@ -867,9 +881,10 @@ def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, h
             check(lib.pe_attention_flashmix(q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
                                             block_table.data_ptr(), table_stride, tok_pos.data_ptr(), tok_row.data_ptr(), _ptr(tiles),
                                             n_runs, T, n_heads, n_kv, head_dim, v_head_dim, window or 0, float(scale), _ptr(sink),
-                                            _ptr(mix), splits, ws.data_ptr(), stream_ptr()), "attention_flashmix", 2)
+                                            _ptr(mix), splits, ws.data_ptr(), _ptr(slopes), keep_first, v_ld, stream_ptr()),
+                  "attention_flashmix", 2)
             return out
-    if q.dtype == torch.bfloat16 and HEADMIX_TENSOR_CORES in ("1", "two-pass") and floats:
+    if q.dtype == torch.bfloat16 and HEADMIX_TENSOR_CORES in ("1", "two-pass") and floats and plain_mask:
         kb = headmix_mma_key_block(n_heads, n_kv, head_dim, v_head_dim)
         if kb:
             # bfloat16: the tensor-core kernel; tiles of 16 tokens, ranges of at least two key blocks
@@ -896,7 +911,8 @@ def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, h
                                    block_table.data_ptr(), table_stride, tok_pos.data_ptr(), tok_row.data_ptr(), _ptr(tiles),
                                    n_runs, PREFILL_TILE, T, n_heads, n_kv, head_dim, v_head_dim, window or 0, float(scale),
                                    _ptr(sink), 0 if sink is None else _code(sink, "sink"), _ptr(mix),
-                                   0 if mix is None else _code(mix, "mix"), qt, splits, ws.data_ptr(), stream_ptr()),
+                                   0 if mix is None else _code(mix, "mix"), qt, splits, ws.data_ptr(), _ptr(slopes), keep_first, v_ld,
+                                   stream_ptr()),
           "attention_headmix", 2 + (splits > 1))
     return out
 
@@ -904,7 +920,7 @@ def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, h
 # ---------------------------------------------------------------------------- gated mixers and routed feed-forwards
 
 LA_ACTIVATIONS = {"none": 0, "silu": 1}
-GATE_ACTIVATIONS = {"none": 0, "sigmoid": 1, "silu": 2, "gelu_tanh": 3}
+GATE_ACTIVATIONS = {"none": 0, "sigmoid": 1, "silu": 2, "gelu_tanh": 3, "relu2": 4}
 
 
 def linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, n_heads: int, head_dim: int, v_head_dim: int,
@@ -1036,34 +1052,183 @@ def gated_act(gate_up: torch.Tensor, activation: str, col_weights: Optional[torc
     return out
 
 
-def moe_route(logits: torch.Tensor, n_experts: int, top_k: int, extra: bool, ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+EXTRA_COLUMN = {False: 0, None: 0, True: 1, "sigmoid": 1, "one": 2}
+
+
+def moe_route(logits: torch.Tensor, n_experts: int, top_k: int, extra, ids: Optional[torch.Tensor] = None,
+              over_all: bool = False, factor: float = 1.0) -> torch.Tensor:
     """Dense routing weights float32 [T, E (+ 1)] from router logits float32 [T, E (+ 1)]: the softmax over each token's ``top_k``
-    largest logits at their places, zero elsewhere; with ``extra`` the last column is sigmoid(its logit).  ``ids`` int32
+    largest logits at their places, zero elsewhere (``over_all``: their entries of the softmax over all experts instead), times
+    ``factor``; with ``extra`` True the last column is sigmoid(its logit), with "one" it is 1 and has no logit.  ``ids`` int32
     [T, top_k] receives the chosen experts."""
     T = logits.shape[0]
+    extra = EXTRA_COLUMN[extra]
     cols = n_experts + (1 if extra else 0)
-    _need(logits, "logits", torch.float32, (T, cols))
+    _need(logits, "logits", torch.float32, (T, n_experts + (1 if extra == 1 else 0)))
     if ids is not None:
         _need(ids, "ids", torch.int32, (T, top_k))
     out = torch.empty(T, cols, dtype=torch.float32, device=logits.device)
-    check(gated().pe_moe_route(logits.data_ptr(), cols, n_experts, top_k, 1 if extra else 0, out.data_ptr(), _ptr(ids), T,
-                               stream_ptr()), "moe_route")
+    check(gated().pe_moe_route(logits.data_ptr(), logits.shape[1], n_experts, top_k, extra, out.data_ptr(), _ptr(ids), T,
+                               1 if over_all else 0, float(factor), stream_ptr()), "moe_route")
     return out
 
 
 MOE_ROUTE_STREAM_MAX_EXPERTS = 256      # MR_MAX_E of csrc/gated_ops.cu
 
 
-def moe_route_stream(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, router: torch.Tensor, n_experts: int, top_k: int,
-                     extra: bool, ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+def moe_route_stream(x: torch.Tensor, norm_weight: Optional[torch.Tensor], eps: float, router: torch.Tensor, n_experts: int, top_k: int,
+                     extra, ids: Optional[torch.Tensor] = None, over_all: bool = False, factor: float = 1.0) -> torch.Tensor:
     """``moe_route`` of the logits router . RMSNorm(x): x float32 [T, K] is the residual stream, ``norm_weight`` [K] the norm's
-    weight, ``router`` float32 [E (+ 1), K]; norm, logits and choice are one kernel, all in float32 (up to 256 experts)."""
+    weight (None: the router reads the stream as it is), ``router`` float32 [E (+ 1), K]; norm, logits and choice are one kernel,
+    all in float32 (up to 256 experts)."""
     T, K = x.shape
+    extra = EXTRA_COLUMN[extra]
     cols = n_experts + (1 if extra else 0)
-    _need(x, "x", torch.float32); _need(norm_weight, "norm_weight", None, (K,)); _need(router, "router", torch.float32, (cols, K))
+    _need(x, "x", torch.float32); _need(router, "router", torch.float32, (n_experts + (1 if extra == 1 else 0), K))
+    if norm_weight is not None:
+        _need(norm_weight, "norm_weight", None, (K,))
     if ids is not None:
         _need(ids, "ids", torch.int32, (T, top_k))
     out = torch.empty(T, cols, dtype=torch.float32, device=x.device)
-    check(gated().pe_moe_route_stream(x.data_ptr(), norm_weight.data_ptr(), _code(norm_weight, "norm_weight"), float(eps), router.data_ptr(),
-                                      K, n_experts, top_k, 1 if extra else 0, out.data_ptr(), _ptr(ids), T, stream_ptr()), "moe_route_stream")
+    check(gated().pe_moe_route_stream(x.data_ptr(), _ptr(norm_weight), 0 if norm_weight is None else _code(norm_weight, "norm_weight"),
+                                      float(eps), router.data_ptr(), K, n_experts, top_k, extra, out.data_ptr(), _ptr(ids), T,
+                                      1 if over_all else 0, float(factor), stream_ptr()), "moe_route_stream")
+    return out
+
+
+def weighted_act(h: torch.Tensor, activation: str, col_weights: torch.Tensor, group: int) -> torch.Tensor:
+    """act(h) [T, I] with column c multiplied by col_weights[t, min(c // group, n - 1)] (float32 [T, n]; a zero weight gives an
+    exact zero): the hidden units of experts without a gate matrix."""
+    T, I = h.shape
+    _need(h, "h")
+    n = col_weights.shape[1]
+    _need(col_weights, "col_weights", torch.float32, (T, n))
+    out = torch.empty_like(h)
+    check(gated().pe_weighted_act(h.data_ptr(), out.data_ptr(), _code(h, "h"), T, I, GATE_ACTIVATIONS[activation], col_weights.data_ptr(),
+                                  group, n, stream_ptr()), "weighted_act")
+    return out
+
+
+# ---------------------------------------------------------------------------- pairs of tokens in the embedding
+
+def embed_pairs(table: torch.Tensor, pairs: torch.Tensor, ids: torch.Tensor, tok_pos: torch.Tensor, tok_row: torch.Tensor,
+                row_first: torch.Tensor, slots: torch.Tensor, prev: torch.Tensor, buckets: int, mul_prev: int, mul_cur: int) -> torch.Tensor:
+    """table[ids] + pairs[(previous * mul_prev + token * mul_cur) mod buckets] as float32 [T, H]; a sequence's first token takes row
+    ``buckets`` of ``pairs``.  ``prev`` int32 [slots, 1] holds every sequence's last token and is brought up to date."""
+    V, H = table.shape
+    T = ids.shape[0]
+    _need(table, "table"); _need(pairs, "pairs", table.dtype, (buckets + 1, H)); _need(ids, "ids", torch.int32, (T,))
+    _need(prev, "prev", torch.int32)
+    out = torch.empty(T, H, dtype=torch.float32, device=table.device)
+    check(core().pe_embed_pairs(table.data_ptr(), pairs.data_ptr(), _code(table, "table"), ids.data_ptr(), tok_pos.data_ptr(),
+                                tok_row.data_ptr(), row_first.data_ptr(), slots.data_ptr(), prev.data_ptr(), prev.stride(0), out.data_ptr(),
+                                T, H, V, buckets, mul_prev, mul_cur, stream_ptr()), "embed_pairs")
+    return out
+
+
+# ---------------------------------------------------------------------------- the state-space mixer
+
+def state_space_elems(n_heads: int, head_dim: int, state: int) -> int:
+    """float32 numbers a sequence's recurrent state takes (the kernel's own order, with its padding rows): the rows of a state
+    column are dealt to the smallest power of two of threads that leaves a thread at most 16 (pe_state_space_elems of
+    csrc/state_space.cu gives the same number)."""
+    ns = 1
+    while (state + ns - 1) // ns > 16 and ns < 32:
+        ns *= 2
+    return n_heads * ((state + ns - 1) // ns) * ns * head_dim
+
+
+def conv_silu(proj: torch.Tensor, col_offset: int, channels: int, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+              state_offset: int, tok_row: torch.Tensor, row_first: torch.Tensor, row_lens: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+    """silu(bias + sum_j w[:, j] u_(t - taps + 1 + j)) as float32 [T, channels] for the inputs u at columns ``col_offset`` .. of
+    proj [T, ld] (packed sequences); inputs before a step's first token come from the sequences' state (float32, (taps - 1) *
+    channels numbers at ``state_offset``), which is then brought up to date."""
+    from .library import state_space
+    T, ld = proj.shape
+    taps = weight.shape[1]
+    _need(proj, "proj"); _need(weight, "weight", None, (channels, taps))
+    if bias is not None:
+        _need(bias, "bias", None, (channels,))
+    sp, stride = _state_args(state, state_offset, (taps - 1) * channels) if taps > 1 else (0, 0)
+    out = torch.empty(T, channels, dtype=torch.float32, device=proj.device)
+    check(state_space().pe_conv_silu(proj.data_ptr(), _code(proj, "proj"), ld, col_offset, channels, taps, weight.data_ptr(),
+                                     _code(weight, "weight"), _ptr(bias), 0 if bias is None else _code(bias, "bias"), sp, stride,
+                                     tok_row.data_ptr(), row_first.data_ptr(), row_lens.data_ptr(), slots.data_ptr(), out.data_ptr(),
+                                     T, slots.shape[0], stream_ptr()), "conv_silu", 2 if taps > 1 else 1)
+    return out
+
+
+def state_space_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_offset: int, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
+                     state: torch.Tensor, state_offset: int, row_first: torch.Tensor, row_lens: torch.Tensor, slots: torch.Tensor,
+                     n_heads: int, head_dim: int, n_state: int, n_groups: int) -> torch.Tensor:
+    """y float32 [T, H * P] of S_t = exp(-exp(A_log) dt) S_(t-1) + dt B_t x_t^T, y_t = S_t^T C_t + D x_t with dt = softplus(raw + bias):
+    x | B | C are the columns of ``xbc`` float32 [T, H*P + 2 G N], the raw step sizes columns ``dt_offset`` .. of proj.  The states
+    come from and return to the sequences' float32 state at ``state_offset``."""
+    from .library import state_space
+    T = xbc.shape[0]
+    H, P, N, G = n_heads, head_dim, n_state, n_groups
+    _need(xbc, "xbc", torch.float32, (T, H * P + 2 * G * N)); _need(proj, "proj")
+    for t, name in ((dt_bias, "dt_bias"), (a_log, "a_log"), (d_skip, "d_skip")):
+        _need(t, name, None, (H,))
+    sp, stride = _state_args(state, state_offset, state_space_elems(H, P, N))
+    y = torch.empty(T, H * P, dtype=torch.float32, device=xbc.device)
+    check(state_space().pe_state_space_scan(xbc.data_ptr(), xbc.shape[1], proj.data_ptr(), _code(proj, "proj"), proj.shape[1], dt_offset,
+                                            dt_bias.data_ptr(), _code(dt_bias, "dt_bias"), a_log.data_ptr(), _code(a_log, "a_log"),
+                                            d_skip.data_ptr(), _code(d_skip, "d_skip"), sp, stride, row_first.data_ptr(),
+                                            row_lens.data_ptr(), slots.data_ptr(), y.data_ptr(), slots.shape[0], H, P, N, G,
+                                            stream_ptr()), "state_space_scan")
+    return y
+
+
+def gate_norm(y: torch.Tensor, group: int, proj: torch.Tensor, gate_offset: int, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """u = y * silu(gate) with the gate at columns ``gate_offset`` .. of proj; every run of ``group`` channels of u divided by its root
+    mean square and multiplied by ``weight`` [C]; [T, C] in proj's dtype.  y float32 [T, C]."""
+    from .library import state_space
+    T, C = y.shape
+    _need(y, "y", torch.float32); _need(proj, "proj"); _need(weight, "weight", None, (C,))
+    out = torch.empty(T, C, dtype=proj.dtype, device=y.device)
+    check(state_space().pe_gate_norm(y.data_ptr(), T, C, group, proj.data_ptr(), _code(proj, "proj"), proj.shape[1], gate_offset,
+                                     weight.data_ptr(), _code(weight, "weight"), float(eps), out.data_ptr(), stream_ptr()), "gate_norm")
+    return out
+
+
+# ---------------------------------------------------------------------------- attention over low-rank rows
+
+def latent_prepare(proj: torch.Tensor, n_heads: int, head_dim: int, rot_dim: int, rank: int, dkv_offset: int, norm_weight: torch.Tensor,
+                   eps: float, freq: Optional[torch.Tensor], rot_dims: int, q_absorbed: torch.Tensor, tok_pos: torch.Tensor,
+                   tok_row: torch.Tensor, k_pool: Optional[torch.Tensor], block_table: Optional[torch.Tensor], table_stride: int) -> torch.Tensor:
+    """Queries [T, H * (rank + rot_dim)] = [absorbed plain part | turned rotated part] a head, from ``q_absorbed`` [H, T, rank] and the
+    rotated parts of the queries in proj [T, ld] (a head = head_dim plain | rot_dim rotated entries); the row [rmsnorm(first rank
+    entries at ``dkv_offset``) * norm_weight | turned last rot_dim entries] goes to the token's place in ``k_pool`` [pages, 1, PAGE,
+    rank + rot_dim] (skipped when None)."""
+    from .library import state_space
+    T, ld = proj.shape
+    H, W = n_heads, rank + rot_dim
+    _need(proj, "proj"); _need(q_absorbed, "q_absorbed", proj.dtype, (H, T, rank)); _need(norm_weight, "norm_weight", None, (rank,))
+    if rot_dims:
+        _need(freq, "freq", torch.float32, (rot_dims // 2,))
+    store = k_pool is not None
+    if store:
+        _need(k_pool, "k_pool", proj.dtype); _need(block_table, "block_table", torch.int32)
+        if tuple(k_pool.shape[1:]) != (1, PAGE, W):
+            raise KernelError(f"the cache pool must be [pages, 1, {PAGE}, {W}], not {tuple(k_pool.shape)}")
+    q = torch.empty(T, H * W, dtype=proj.dtype, device=proj.device)
+    check(state_space().pe_latent_prepare(proj.data_ptr(), _code(proj, "proj"), ld, T, H, head_dim, rot_dim, rank, dkv_offset,
+                                          norm_weight.data_ptr(), _code(norm_weight, "norm_weight"), float(eps), _ptr(freq), rot_dims,
+                                          q_absorbed.data_ptr(), q.data_ptr(), tok_pos.data_ptr(), tok_row.data_ptr(), _ptr(k_pool),
+                                          _ptr(block_table), table_stride, 1 if store else 0, stream_ptr()), "latent_prepare")
+    return q
+
+
+def head_gate(o: torch.Tensor, proj: Optional[torch.Tensor], gate_offset: int) -> torch.Tensor:
+    """[T, H * Dv] from o [H, T, Dv] (head-major, as a batched product leaves it), head h of token t multiplied by
+    sigmoid(proj[t, gate_offset + h]) (proj None: no gate)."""
+    from .library import state_space
+    H, T, Dv = o.shape
+    _need(o, "o")
+    if proj is not None:
+        _need(proj, "proj", o.dtype)
+    out = torch.empty(T, H * Dv, dtype=o.dtype, device=o.device)
+    check(state_space().pe_head_gate(o.data_ptr(), _code(o, "o"), _ptr(proj), 0 if proj is None else proj.shape[1], gate_offset, T, H, Dv,
+                                     out.data_ptr(), stream_ptr()), "head_gate")
     return out

@@ -24,10 +24,14 @@ MIXER_SOURCES = ("layernorm_conv.cu", "attention_headmix.cu", "attention_headmix
 # The kernels of gated mixers and routed feed-forwards (the linear-attention recurrence, rotation of pairs with unit norm and
 # cache write, norms over groups of channels with a gate, sums of normed branches, gated activations, the choice of experts).
 GATED_SOURCES = ("linear_attention.cu", "gated_ops.cu")
+# The kernels of the state-space mixer (short convolution with silu, the recurrence with a scalar decay, gate then norm) and of
+# attention over one low-rank row per position.
+STATE_SOURCES = ("state_space.cu", "latent_ops.cu")
 HEAD_DIM_SOURCES = ("attention_decode.cu", "attention_prefill.cu", "attention_prefill_tcgen05.cu")      # compiled per head size
 
 _SIGNATURES = {
     "pe_embed": [P, I, P, P, I, I, I, P],
+    "pe_embed_pairs": [P, P, I, P, P, P, P, P, P, LL, P, I, I, I, I, I, I, P],
     "pe_select_tokens": [P, P, P, I, P],
     "pe_rmsnorm": [P, P, P, I, F, P, I, I, I, P],
     "pe_add_rmsnorm": [P, P, I, P, I, F, P, I, I, I, P],
@@ -56,9 +60,9 @@ _MIXER_SIGNATURES = {
     "pe_conv_state_update": [P, P, LL, P, P, P, I, I, I, P],
     "pe_dual_layernorm_conv": [P, P, I, P, I, P, I, P, P, P, I, P, I, P, I, P, P, I, LL, P, P, P, P, F, I, I, I, I, I, P],
     "pe_mingru": [P, I, P, LL, P, P, P, P, P, I, I, I, I, P, P],
-    "pe_attention_headmix": [P, I, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, I, F, P, I, P, I, I, I, P, P],
+    "pe_attention_headmix": [P, I, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, I, F, P, I, P, I, I, I, P, P, I, I, P],
     "pe_qknorm_store": [P, I, I, I, I, I, I, P, I, P, I, F, P, P, P, P, P, I, I, P],
-    "pe_attention_flashmix": [P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P, I, P, P],
+    "pe_attention_flashmix": [P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P, I, P, P, I, I, P],
     "pe_attention_headmix_mma": [P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, P, P, I, P, P],
 }
 
@@ -70,8 +74,17 @@ _GATED_SIGNATURES = {
     "pe_scaled_add": [P, P, I, F, LL, P],
     "pe_add_rows": [P, P, P, I, I, I, P],
     "pe_gated_act": [P, P, I, I, I, I, P, I, I, P],
-    "pe_moe_route": [P, I, I, I, I, P, P, I, P],
-    "pe_moe_route_stream": [P, P, I, F, P, I, I, I, I, P, P, I, P],
+    "pe_weighted_act": [P, P, I, I, I, I, P, I, I, P],
+    "pe_moe_route": [P, I, I, I, I, P, P, I, I, F, P],
+    "pe_moe_route_stream": [P, P, I, F, P, I, I, I, I, P, P, I, I, F, P],
+}
+
+_STATE_SIGNATURES = {
+    "pe_conv_silu": [P, I, I, I, I, I, P, I, P, I, P, LL, P, P, P, P, P, I, I, P],
+    "pe_state_space_scan": [P, I, P, I, I, I, P, I, P, I, P, I, P, LL, P, P, P, P, I, I, I, I, I, P],
+    "pe_gate_norm": [P, I, I, I, P, I, I, I, P, I, F, P, P],
+    "pe_latent_prepare": [P, I, I, I, I, I, I, I, I, P, I, F, P, I, P, P, P, P, P, P, I, I, P],
+    "pe_head_gate": [P, I, P, I, I, I, I, I, P, P],
 }
 
 _EXTRA_SIGNATURES = {
@@ -169,6 +182,24 @@ def gated() -> ctypes.CDLL:
         lib.pe_linear_attention_scratch_floats.restype = c_longlong
         _gated = lib
     return _gated
+
+
+_state = None
+
+
+def state_space() -> ctypes.CDLL:
+    """The library of the kernels of the state-space mixer and of attention over low-rank rows; compiled at the first call."""
+    global _state
+    if _state is None:
+        lib = build.load("state", STATE_SOURCES)
+        declare(lib, _STATE_SIGNATURES)
+        lib.pe_set_pdl(0 if os.environ.get("PICO_ENGINE_PDL", "1") == "0" else 1)
+        lib.pe_state_space_split.argtypes = [I]
+        lib.pe_state_space_split.restype = c_int
+        lib.pe_state_space_elems.argtypes = [I, I, I]
+        lib.pe_state_space_elems.restype = c_longlong
+        _state = lib
+    return _state
 
 
 _extras = None

@@ -14,11 +14,14 @@ from .linear_attention import LinearAttention
 from .attention_gated import GatedAttention
 from .branch_sum import BranchSum
 from .mixture import Mixture
-from .block import Layer, parallel, pre_norm
+from .attention_latent import LatentAttention
+from .state_space import StateSpace
+from .block import Layer, parallel, post_norm, pre_norm
 from .model import DecoderModel
 
 __all__ = ["ARRANGEMENTS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "FeedForward", "KVView", "Mixer", "Norm",
            "Part", "Position", "StepContext", "build_part", "register_arrangement", "register_feed_forward",
            "register_mixer", "register_norm", "register_position", "RMSNorm", "NoPosition", "RotaryHalf",
            "GQAAttention", "SwiGLU", "Layer", "pre_norm", "DecoderModel", "LayerNorm", "SinusoidAdd", "CausalConvAdd",
-           "HeadMixAttention", "MinGRU", "DenseMLP", "parallel", "GatedMLP", "LinearAttention", "GatedAttention", "BranchSum", "Mixture"]
+           "HeadMixAttention", "MinGRU", "DenseMLP", "parallel", "GatedMLP", "LinearAttention", "GatedAttention", "BranchSum", "Mixture",
+           "LatentAttention", "StateSpace", "post_norm"]

@@ -36,31 +36,55 @@ class GatedAttention(Mixer):
         if spec.window is not None and spec.window <= 0:
             raise ConfigError(f"window {spec.window} must be positive")
         self.state_offset = 0
-        self.w_in = self.w_o = self.freq = None
-        # the kernels of grouped attention take equal key and value sizes: any up to 256 in float32, multiples of 16 in bfloat16
-        self.plain_kernels = spec.v_head_dim == spec.head_dim and (dtype == torch.float32 or spec.head_dim % 16 == 0)
+        if spec.distance_slopes is not None and len(spec.distance_slopes) != spec.n_heads:
+            raise ConfigError(f"{len(spec.distance_slopes)} distance slopes for {spec.n_heads} heads")
+        if spec.keep_first < 0 or (spec.keep_first and spec.window is None):
+            raise ConfigError("keep_first belongs to a window and cannot be negative")
+        self.w_in = self.w_o = self.freq = self.b_in = self.b_o = self.slopes = None
+        # the kernels of grouped attention take equal key and value sizes: any up to 256 in float32, multiples of 16 in bfloat16;
+        # a distance bias and kept first keys are known to the kernels that take two sizes
+        self.plain_kernels = (spec.v_head_dim == spec.head_dim and (dtype == torch.float32 or spec.head_dim % 16 == 0)
+                              and spec.distance_slopes is None and not spec.keep_first)
 
     def _widths(self):
         s = self.spec
         return s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim, s.n_kv_heads * s.v_head_dim, s.n_heads * s.v_head_dim
 
+    def _in_names(self):
+        """The matrices of the first product, in the order of its columns: q, then k and v where the mixer has its own, then the gate."""
+        s = self.spec
+        return [s.q_name] + ([s.k_name, s.v_name] if s.own_kv else []) + ([s.gate] if s.gate is not None else [])
+
     def expected_tensors(self):
         s, p = self.spec, self.spec.prefix
         q, k, v, o = self._widths()
-        out = {p + s.q_name: ParamSpec((q, s.hidden)), p + s.k_name: ParamSpec((k, s.hidden)), p + s.v_name: ParamSpec((v, s.hidden)),
-               p + s.o_name: ParamSpec((s.hidden, o))}
-        if s.gate is not None:
-            out[p + s.gate] = ParamSpec((o, s.hidden))
+        rows = {s.q_name: q, s.k_name: k, s.v_name: v, s.gate: o}
+        out = {p + n: ParamSpec((rows[n], s.hidden)) for n in self._in_names()}
+        out[p + s.o_name] = ParamSpec((s.hidden, o))
+        if s.bias:
+            out.update({p + n + s.bias_suffix: ParamSpec((rows[n],), init="normal") for n in self._in_names() if n != s.gate})
+            out[p + s.o_name + s.bias_suffix] = ParamSpec((s.hidden,), init="normal")
         return out
 
     def take_tensors(self, get):
         s, p = self.spec, self.spec.prefix
-        parts = [get(p + n) for n in (s.q_name, s.k_name, s.v_name)] + ([get(p + s.gate)] if s.gate is not None else [])
+        parts = [get(p + n) for n in self._in_names()]
         rows = sum(t.shape[0] for t in parts)
-        if rows % 8:                                       # rows of the product stay aligned for the attention kernels' vector loads
-            parts.append(torch.zeros(8 - rows % 8, s.hidden, dtype=parts[0].dtype, device=parts[0].device))
+        pad = (8 - rows % 8) % 8                           # rows of the product stay aligned for the attention kernels' vector loads
+        if pad:
+            parts.append(torch.zeros(pad, s.hidden, dtype=parts[0].dtype, device=parts[0].device))
         self.w_in = torch.cat(parts, dim=0).contiguous()
         self.w_o = get(p + s.o_name)
+        if s.bias:
+            like = parts[0]
+            biases = [get(p + n + s.bias_suffix) if n != s.gate else torch.zeros(get(p + n).shape[0], dtype=like.dtype, device=like.device)
+                      for n in self._in_names()]
+            if pad:
+                biases.append(torch.zeros(pad, dtype=like.dtype, device=like.device))
+            self.b_in = torch.cat([b.to(like.dtype) for b in biases]).contiguous()
+            self.b_o = get(p + s.o_name + s.bias_suffix)
+        if s.distance_slopes is not None:
+            self.slopes = torch.tensor(s.distance_slopes, dtype=torch.float32, device=self.device)
 
     def prepare(self, max_positions):
         from ..ops.library import for_head_dim, gated, mixers
@@ -73,36 +97,49 @@ class GatedAttention(Mixer):
             self.freq = pair_frequencies(self.spec.position, self.device)
 
     def weights(self):
-        return [self.w_in, self.w_o]
+        return [t for t in (self.w_in, self.w_o, self.b_in, self.b_o) if t is not None]
 
     def cache_needs(self):
         s = self.spec
-        return CacheNeeds(kv=KVNeed(s.n_kv_heads, s.head_dim, s.window,
-                                    v_head_dim=None if s.v_head_dim == s.head_dim else s.v_head_dim))
+        if not s.own_kv:
+            return CacheNeeds()
+        window, keep = s.cache_span if s.cache_span is not None else (s.window, s.keep_first)
+        return CacheNeeds(kv=KVNeed(s.n_kv_heads, s.head_dim, window, v_head_dim=None if s.v_head_dim == s.head_dim else s.v_head_dim,
+                                    keep_first=keep if window is not None else 0))
 
     def gated_heads(self, h, ctx, cache_entry, owns_cache, x_norm=None):
         """The heads' outputs times the gate [T, n_heads * v_head_dim] for normed rows h (or ``x_norm`` = (stream, its norm))."""
         s = self.spec
         q_w, k_w, v_w, o_w = self._widths()
+        if owns_cache != s.own_kv:
+            raise ConfigError("an attention without key and value projections reads another entry's cache, one with them writes its own")
         kv = ctx.kv(cache_entry)
-        proj = first_product(*normed_rows(h, x_norm, ctx, self.w_in), self.w_in, ctx)
+        if self.b_in is not None:
+            proj = linear(h if h is not None else x_norm[1].forward(x_norm[0], ctx.dtype), self.w_in, self.b_in, out_dtype=ctx.dtype)
+        else:
+            proj = first_product(*normed_rows(h, x_norm, ctx, self.w_in), self.w_in, ctx)
         rot_dims = s.position.dims if isinstance(s.position, RotaryPairsSpec) else 0
-        kernels.rotary_norm_store(proj, s.n_heads, s.n_kv_heads, s.head_dim, s.v_head_dim, self.freq, rot_dims, s.qk_unit_norm,
-                                  s.norm_eps, ctx.tok_pos, ctx.tok_row, kv.k if owns_cache else None, kv.v if owns_cache else None,
-                                  kv.table if owns_cache else None, kv.stride)
+        n_kv = s.n_kv_heads if s.own_kv else 0             # a row of proj then has no key and value entries
+        if rot_dims or s.qk_unit_norm or owns_cache:
+            kernels.rotary_norm_store(proj, s.n_heads, n_kv, s.head_dim, s.v_head_dim, self.freq, rot_dims, s.qk_unit_norm,
+                                      s.norm_eps, ctx.tok_pos, ctx.tok_row, kv.k if owns_cache else None, kv.v if owns_cache else None,
+                                      kv.table if owns_cache else None, kv.stride)
         if self.plain_kernels:
             a = kernels.attention(proj, proj.shape[1], s.n_heads, s.n_kv_heads, s.head_dim, kv.k, kv.v, kv.table, kv.stride,
                                   ctx.tok_pos, ctx.tok_row, s.window, s.scale, ctx, own_rows_only=owns_cache)
         else:
             a = kernels.attention_headmix(proj, proj.shape[1], s.n_heads, s.n_kv_heads, s.head_dim, s.v_head_dim, kv.k, kv.v,
-                                          kv.table, kv.stride, ctx.tok_pos, ctx.tok_row, s.window, s.scale, None, None, ctx)
+                                          kv.table, kv.stride, ctx.tok_pos, ctx.tok_row, s.window, s.scale, None, None, ctx,
+                                          slopes=self.slopes, keep_first=s.keep_first)
         if s.gate is None:
             return a
-        return kernels.gated_norm(a, 0, None, s.norm_eps, proj, q_w + k_w + v_w, "sigmoid", ctx.dtype)
+        return kernels.gated_norm(a, 0, None, s.norm_eps, proj, q_w + (k_w + v_w if s.own_kv else 0), "sigmoid", ctx.dtype)
 
     def apply(self, h, ctx, entry, cache_entry, owns_cache, out_dtype=None, x_norm=None):
-        return linear(self.gated_heads(h, ctx, cache_entry, owns_cache, x_norm), self.w_o, out_dtype=out_dtype or ctx.dtype)
+        return linear(self.gated_heads(h, ctx, cache_entry, owns_cache, x_norm), self.w_o, self.b_o, out_dtype=out_dtype or ctx.dtype)
 
     def add_normed_to(self, x, norm, scale, ctx, entry, cache_entry, owns_cache) -> bool:
+        if self.b_o is not None:
+            return False                                   # the fused sum has no place for a bias
         last_product_into(x, self.gated_heads(None, ctx, cache_entry, owns_cache, (x, norm)), self.w_o, scale, ctx)
         return True

@@ -1,0 +1,97 @@
+"""Softmax attention over one low-rank row per position: the cache keeps the normed latent row and one rotated key part."""
+from __future__ import annotations
+
+import torch
+
+from ..cache import CacheNeeds, KVNeed
+from ..config.specs import ConfigError, LatentAttentionSpec, RotaryPairsSpec
+from ..ops import kernels, linear
+from ..weights.loader import ParamSpec
+from .attention_gated import pair_frequencies
+from .base import Mixer, register_mixer
+
+
+@register_mixer(LatentAttentionSpec)
+class LatentAttention(Mixer):
+    """A head's plain key is W_uk,h c for the latent row c of a position, so q_plain . k_plain = (W_uk,h^T q_plain) . c: the
+    queries are carried into the latent space (a product a head, batched over the heads), and attention then reads the cached
+    rows [c | rotated key part] as they are, as one key head of size rank + rot_dim whose first ``rank`` entries are also the
+    value.  What comes out, sum_j p_j c_j a head, meets W_uv,h in a second batched product; the heads are multiplied by the
+    sigmoid of their gate logit and projected by W_o.
+
+    One product makes q, the down projection and the gate logits.  The norm of the latent row, the rotation (angles from float32
+    positions and float32 frequencies), the scores, the softmax and the gate are float32 in either dtype
+    (csrc/latent_ops.cu, csrc/attention_headmix*.cu)."""
+
+    takes_out_dtype = True
+
+    def __init__(self, spec: LatentAttentionSpec, dtype, device):
+        super().__init__(spec, dtype, device)
+        if not isinstance(spec.position, RotaryPairsSpec) or spec.position.head_dim != spec.rot_dim:
+            raise ConfigError("latent attention rotates pairs of its rot_dim entries")
+        if spec.position.dims > spec.rot_dim or spec.position.dims % 2:
+            raise ConfigError(f"{spec.position.dims} rotated entries do not fit the rotated part of {spec.rot_dim}")
+        if spec.kv_rank + spec.rot_dim > 1024:
+            raise ConfigError(f"a cached row of {spec.kv_rank + spec.rot_dim} entries is not taken: up to 1024 are")
+        self.state_offset = 0
+        self.w_in = self.w_uk = self.w_uv = self.w_o = self.dkv_norm = self.freq = None
+
+    def _widths(self):
+        s = self.spec
+        return s.n_heads * (s.head_dim + s.rot_dim), s.kv_rank + s.rot_dim, s.n_heads if s.gate is not None else 0
+
+    def expected_tensors(self):
+        s, p = self.spec, self.spec.prefix
+        q, dkv, g = self._widths()
+        out = {p + s.q_name: ParamSpec((q, s.hidden)), p + s.dkv_name: ParamSpec((dkv, s.hidden)),
+               p + s.dkv_norm: ParamSpec((s.kv_rank,), init="one_plus_normal"),
+               p + s.uk_name: ParamSpec((s.n_heads * s.head_dim, s.kv_rank)), p + s.uv_name: ParamSpec((s.n_heads * s.v_head_dim, s.kv_rank)),
+               p + s.o_name: ParamSpec((s.hidden, s.n_heads * s.v_head_dim))}
+        if s.gate is not None:
+            out[p + s.gate] = ParamSpec((g, s.hidden))
+        return out
+
+    def take_tensors(self, get):
+        s, p = self.spec, self.spec.prefix
+        parts = [get(p + s.q_name), get(p + s.dkv_name)] + ([get(p + s.gate)] if s.gate is not None else [])
+        rows = sum(t.shape[0] for t in parts)
+        if rows % 8:
+            parts.append(torch.zeros(8 - rows % 8, s.hidden, dtype=parts[0].dtype, device=parts[0].device))
+        self.w_in = torch.cat(parts, dim=0).contiguous()
+        self.w_uk = get(p + s.uk_name).view(s.n_heads, s.head_dim, s.kv_rank).contiguous()          # [H, D, rank]: q_plain @ W_uk,h
+        self.w_uv = get(p + s.uv_name).view(s.n_heads, s.v_head_dim, s.kv_rank).transpose(1, 2).contiguous()   # [H, rank, Dv]
+        self.w_o = get(p + s.o_name)
+        self.dkv_norm = get(p + s.dkv_norm)
+
+    def prepare(self, max_positions):
+        from ..ops.library import mixers, state_space
+        state_space()                                      # build or load this part's kernels now, loudly
+        mixers()
+        self.freq = pair_frequencies(self.spec.position, self.device) if self.spec.position.dims else None
+
+    def weights(self):
+        return [self.w_in, self.w_uk, self.w_uv, self.w_o, self.dkv_norm]
+
+    def cache_needs(self):
+        s = self.spec
+        return CacheNeeds(kv=KVNeed(1, s.kv_rank + s.rot_dim, None, v_heads=0))
+
+    def gated_heads(self, h, ctx, cache_entry, owns_cache):
+        s = self.spec
+        H, D, R, rank = s.n_heads, s.head_dim, s.rot_dim, s.kv_rank
+        q_w, dkv_w, _ = self._widths()
+        T = h.shape[0]
+        kv = ctx.kv(cache_entry)
+        proj = linear(h, self.w_in, out_dtype=ctx.dtype)
+        # the plain parts of the queries, head-major, times W_uk: [H, T, D] x [H, D, rank]
+        q_plain = proj[:, :q_w].view(T, H, D + R)[:, :, :D].transpose(0, 1)
+        q_latent = torch.bmm(q_plain, self.w_uk)
+        q = kernels.latent_prepare(proj, H, D, R, rank, q_w, self.dkv_norm, s.norm_eps, self.freq, s.position.dims, q_latent,
+                                   ctx.tok_pos, ctx.tok_row, kv.k if owns_cache else None, kv.table if owns_cache else None, kv.stride)
+        a = kernels.attention_headmix(q, q.shape[1], H, 1, rank + R, rank, kv.k, None, kv.table, kv.stride, ctx.tok_pos, ctx.tok_row,
+                                      None, s.scale, None, None, ctx, values_in_keys=True)
+        o = torch.bmm(a.view(T, H, rank).transpose(0, 1), self.w_uv)                        # [H, T, Dv]
+        return kernels.head_gate(o, proj if s.gate is not None else None, q_w + dkv_w)
+
+    def apply(self, h, ctx, entry, cache_entry, owns_cache, out_dtype=None):
+        return linear(self.gated_heads(h, ctx, cache_entry, owns_cache), self.w_o, out_dtype=out_dtype or ctx.dtype)

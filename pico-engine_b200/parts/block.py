@@ -4,7 +4,8 @@ from __future__ import annotations
 
 from ..config.specs import ConfigError, LayerSpec
 from ..cache import CacheNeeds
-from .base import ARRANGEMENTS, FEED_FORWARDS, INPUT_FILTERS, MIXERS, NORMS, Norm, build_part, register_arrangement
+from ..weights.loader import ParamSpec
+from .base import ARRANGEMENTS, FEED_FORWARDS, INPUT_FILTERS, MIXERS, NORMS, Norm, Part, build_part, register_arrangement
 
 
 class PassThrough(Norm):
@@ -16,6 +17,39 @@ class PassThrough(Norm):
     def forward(self, x, out_dtype, rows_index=None):
         rows = x if rows_index is None else x.index_select(0, rows_index.long())
         return rows.to(out_dtype)
+
+
+class ScaleVector(Part):
+    """A learned vector [hidden] that a sublayer's normed output is multiplied by before it is added to the stream."""
+
+    def __init__(self, name: str, size: int, dtype, device):
+        super().__init__(None, dtype, device)
+        self.name, self.size, self.vector = name, size, None
+        self.folded = {}
+
+    def expected_tensors(self):
+        return {self.name: ParamSpec((self.size,), init="one_plus_normal")}
+
+    def take_tensors(self, get):
+        self.vector = get(self.name)
+
+    def weights(self):
+        return [self.vector]
+
+    def times(self, norm_weight):
+        """norm weight * this vector, element by element, formed once in float32."""
+        key = norm_weight.data_ptr()
+        if key not in self.folded:
+            self.folded[key] = (norm_weight.float() * self.vector.float()).contiguous()
+        return self.folded[key]
+
+
+def _hidden_of(spec: LayerSpec) -> int:
+    for part in (spec.mixer_norm, spec.feed_forward_norm, spec.mixer, spec.feed_forward):
+        for field in ("size", "hidden"):
+            if part is not None and hasattr(part, field):
+                return getattr(part, field)
+    raise ConfigError("a scaled sublayer output needs a part that knows the stream's width")
 
 
 class Layer:
@@ -32,6 +66,9 @@ class Layer:
         self.feed_forward_norm = build(NORMS, "norm", spec.feed_forward_norm) or PassThrough(dtype, device)
         self.mixer_input = build(INPUT_FILTERS, "input filter", spec.mixer_input)
         self.feed_forward_input = build(INPUT_FILTERS, "input filter", spec.feed_forward_input)
+        self.mixer_scale = None if spec.mixer_scale is None else ScaleVector(spec.mixer_scale, _hidden_of(spec), dtype, device)
+        self.feed_forward_scale = None if spec.feed_forward_scale is None else \
+            ScaleVector(spec.feed_forward_scale, _hidden_of(spec), dtype, device)
         if (self.mixer_input is not None and self.mixer is None) or (self.feed_forward_input is not None and self.feed_forward is None):
             raise ConfigError("an input filter needs the sublayer whose input it filters")
         try:
@@ -42,7 +79,8 @@ class Layer:
     def parts(self):
         """The parts that are there (a stand-in for an absent norm has no tensors and is left out)."""
         return tuple(p for p in (self.mixer, self.mixer_norm, self.mixer_input, self.feed_forward, self.feed_forward_norm,
-                                 self.feed_forward_input) if p is not None and not isinstance(p, PassThrough))
+                                 self.feed_forward_input, self.mixer_scale, self.feed_forward_scale)
+                     if p is not None and not isinstance(p, PassThrough))
 
     def cache_needs(self):
         """What one execution of the layer keeps in the cache: the mixer's keys, values and state, and behind the
@@ -135,3 +173,31 @@ def parallel(layer: Layer, x, ctx, entry, cache_entry, owns_cache) -> None:
             part.add_output_to(x, h, ctx)
         else:
             kernels.residual_add(x, part.apply(h, ctx).contiguous())
+
+
+@register_arrangement("post_norm")
+def post_norm(layer: Layer, x, ctx, entry, cache_entry, owns_cache) -> None:
+    """x += s1 * norm1(mixer(x)); x += s2 * norm2(feed_forward(x)): the sublayers read the stream as it is (rounded to the
+    step's dtype where that is not float32), the norms act on their outputs, s1 and s2 are learned vectors (absent: ones).
+    A sublayer hands over the float32 sums of its last product; norm, scale and the sum into the stream are one kernel in
+    float32.  A feed-forward that routes is also handed the float32 stream, so that its router reads that."""
+    from ..ops import kernels
+    from .norm import RMSNorm
+    ctx.settle(x)
+    halves = ((layer.mixer, layer.mixer_norm, layer.mixer_scale, (entry, cache_entry, owns_cache)),
+              (layer.feed_forward, layer.feed_forward_norm, layer.feed_forward_scale, ()))
+    reads = PassThrough(ctx.dtype, x.device)
+    for part, norm, scale, where in halves:
+        if part is None:
+            continue
+        if type(norm) is not RMSNorm:
+            raise ConfigError("the post_norm arrangement takes an RMS norm on every sublayer's output")
+        h = reads.forward(x, ctx.dtype)
+        extra = {"out_dtype": x.dtype} if getattr(part, "takes_out_dtype", False) else {}
+        if part is layer.feed_forward and getattr(part, "routes_from_stream", False):
+            extra["x_norm"] = (x, reads)
+        y = part.apply(h, ctx, *where, **extra)
+        if y.dtype != x.dtype:
+            y = y.float()
+        kernels.normed_sum_add(x, [y.contiguous()], [norm.weight.float().contiguous() if scale is None else scale.times(norm.weight)],
+                               norm.eps, 1.0)

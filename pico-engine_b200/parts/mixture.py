@@ -1,4 +1,4 @@
-"""A mixture of gated feed-forward experts with a router and an optional shared expert."""
+"""A mixture of feed-forward experts (gated or not) with a router and an optional shared expert."""
 from __future__ import annotations
 
 import torch
@@ -24,6 +24,7 @@ class Mixture(FeedForward):
     the necessary arithmetic for long prompts."""
 
     takes_out_dtype = True      # apply(..., out_dtype=) gives the product's float32 sums where the caller goes on in float32
+    routes_from_stream = True   # apply(..., x_norm=(stream, norm)) lets the router read the float32 stream
 
     def __init__(self, spec: MixtureSpec, dtype, device):
         super().__init__(spec, dtype, device)
@@ -31,6 +32,8 @@ class Mixture(FeedForward):
             raise ConfigError(f"top_k = {spec.top_k} must lie in 1 .. n_experts = {spec.n_experts}")
         if spec.activation not in kernels.GATE_ACTIVATIONS:
             raise ConfigError(f"activation {spec.activation!r} is not known")
+        if spec.scores not in ("softmax_chosen", "softmax_all"):
+            raise ConfigError(f"scores must be \"softmax_chosen\" or \"softmax_all\", not {spec.scores!r}")
         self.w_router = self.w_gate_up = self.w_down = None
 
     def _experts(self):
@@ -40,22 +43,31 @@ class Mixture(FeedForward):
             names.append((s.prefix + s.shared_name + ".", s.shared_intermediate))
         return names
 
+    def _shared_gate(self) -> bool:
+        return self.spec.shared_intermediate is not None and self.spec.shared_gate_name is not None
+
+    def _extra(self):
+        """What the routing kernels make of the column behind the experts': nothing, sigmoid(gate logit), or 1."""
+        return False if self.spec.shared_intermediate is None else (True if self._shared_gate() else "one")
+
     def expected_tensors(self):
         s = self.spec
         out = {s.prefix + s.router_name: ParamSpec((s.n_experts, s.hidden))}
         for p, ff in self._experts():
-            out.update({p + s.gate_name: ParamSpec((ff, s.hidden)), p + s.up_name: ParamSpec((ff, s.hidden)),
-                        p + s.down_name: ParamSpec((s.hidden, ff))})
-        if s.shared_intermediate is not None:
+            if s.gated:
+                out[p + s.gate_name] = ParamSpec((ff, s.hidden))
+            out.update({p + s.up_name: ParamSpec((ff, s.hidden)), p + s.down_name: ParamSpec((s.hidden, ff))})
+        if self._shared_gate():
             out[s.prefix + s.shared_gate_name] = ParamSpec((1, s.hidden))
         return out
 
     def take_tensors(self, get):
         s = self.spec
-        router = [get(s.prefix + s.router_name)] + ([get(s.prefix + s.shared_gate_name)] if s.shared_intermediate is not None else [])
+        router = [get(s.prefix + s.router_name)] + ([get(s.prefix + s.shared_gate_name)] if self._shared_gate() else [])
         self.w_router = torch.cat(router, dim=0).float().contiguous()           # router logits are float32 products
         experts = self._experts()
-        self.w_gate_up = torch.cat([get(p + s.gate_name) for p, _ in experts] + [get(p + s.up_name) for p, _ in experts], dim=0).contiguous()
+        gates = [get(p + s.gate_name) for p, _ in experts] if s.gated else []
+        self.w_gate_up = torch.cat(gates + [get(p + s.up_name) for p, _ in experts], dim=0).contiguous()
         self.w_down = torch.cat([get(p + s.down_name) for p, _ in experts], dim=1).contiguous()
 
     def prepare(self, max_positions):
@@ -66,26 +78,35 @@ class Mixture(FeedForward):
         """Dense weights float32 [T, n_experts (+ 1)] of rows h."""
         s = self.spec
         logits = linear(h, self.w_router, out_dtype=torch.float32)
-        return kernels.moe_route(logits, s.n_experts, s.top_k, s.shared_intermediate is not None)
+        return kernels.moe_route(logits, s.n_experts, s.top_k, self._extra(), over_all=s.scores == "softmax_all", factor=s.route_scale)
 
     def _activation(self, h, ctx, x_norm=None):
         s = self.spec
+        from .block import PassThrough
         from .norm import RMSNorm
-        if x_norm is not None and type(x_norm[1]) is RMSNorm and s.n_experts <= kernels.MOE_ROUTE_STREAM_MAX_EXPERTS:
-            # the router reads the float32 stream itself (its norm is part of the routing kernel): the same logits however
-            # the step is cut, and the gate/up product may take the norm into its prologue
+        how = {"over_all": s.scores == "softmax_all", "factor": s.route_scale}
+        if x_norm is not None and type(x_norm[1]) in (RMSNorm, PassThrough) and s.n_experts <= kernels.MOE_ROUTE_STREAM_MAX_EXPERTS:
+            # the router reads the float32 stream itself (its norm, where it has one, is part of the routing kernel): the same
+            # logits however the step is cut, and the gate/up product may take the norm into its prologue
             x, norm = x_norm
-            weights = kernels.moe_route_stream(x, norm.weight, norm.eps, self.w_router, s.n_experts, s.top_k, s.shared_intermediate is not None)
-            gate_up = first_product(*normed_rows(None, x_norm, ctx, self.w_gate_up), self.w_gate_up, ctx)
+            if type(norm) is RMSNorm:
+                weights = kernels.moe_route_stream(x, norm.weight, norm.eps, self.w_router, s.n_experts, s.top_k, self._extra(), **how)
+                gate_up = first_product(*normed_rows(None, x_norm, ctx, self.w_gate_up), self.w_gate_up, ctx)
+            else:
+                weights = kernels.moe_route_stream(x, None, 0.0, self.w_router, s.n_experts, s.top_k, self._extra(), **how)
+                gate_up = linear(norm.forward(x, ctx.dtype) if h is None else h, self.w_gate_up, out_dtype=ctx.dtype)
         else:
             if h is None:
                 h = x_norm[1].forward(x_norm[0], ctx.dtype)
             weights = self.routing(h)
             gate_up = linear(h, self.w_gate_up, out_dtype=ctx.dtype)
+        if not s.gated:
+            return kernels.weighted_act(gate_up, s.activation, weights, s.intermediate)
         return kernels.gated_act(gate_up, s.activation, weights, s.intermediate)
 
-    def apply(self, h, ctx, out_dtype=None):
-        return linear(self._activation(h, ctx), self.w_down, out_dtype=out_dtype or ctx.dtype)
+    def apply(self, h, ctx, out_dtype=None, x_norm=None):
+        """``x_norm`` = (float32 stream, its norm or pass-through): the router then reads the stream itself."""
+        return linear(self._activation(h, ctx, x_norm), self.w_down, out_dtype=out_dtype or ctx.dtype)
 
     def add_normed_to(self, x, norm, scale, ctx) -> bool:
         """x += scale * mixture(norm(x)); the sum is the last product's epilogue where it takes the sizes."""

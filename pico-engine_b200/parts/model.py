@@ -28,6 +28,7 @@ class DecoderModel:
         self.stream_vectors: Dict[str, torch.Tensor] = {}      # [rows, hidden] tensors whose rows schedule entries add to the stream
         self._keeps_embedding = any(e.add_embedding for e in plan.schedule)
         self.embedding: Optional[torch.Tensor] = None
+        self.pair_table: Optional[torch.Tensor] = None         # rows added to the embedding by (previous token, token)
         self.head: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------ weights
@@ -47,6 +48,8 @@ class DecoderModel:
             out[p.head] = ParamSpec((p.vocab_size, p.hidden_size))
         for name, rows in p.stream_vectors:
             out[name] = ParamSpec((rows, p.hidden_size))
+        if p.embedding_pairs is not None:
+            out[p.embedding_pairs.table] = ParamSpec((p.embedding_pairs.buckets + 1, p.hidden_size))
         return out
 
     def take_tensors(self, get) -> None:
@@ -55,6 +58,8 @@ class DecoderModel:
             part.take_tensors(get)
         self.head = self.embedding if self.plan.head is None else get(self.plan.head)
         self.stream_vectors = {name: get(name) for name, _ in self.plan.stream_vectors}
+        if self.plan.embedding_pairs is not None:
+            self.pair_table = get(self.plan.embedding_pairs.table).to(self.embedding.dtype).contiguous()
 
     def prepare(self, max_positions: int) -> None:
         for part in self._parts():
@@ -62,13 +67,22 @@ class DecoderModel:
 
     # ------------------------------------------------------------------ cache
     def cache_needs(self) -> List[Optional[CacheNeeds]]:
-        """Per schedule entry; None for an entry that reads another entry's cache."""
-        return [None if e.cache_of is not None else self.layers[e.layer].cache_needs() for e in self.plan.schedule]
+        """Per schedule entry; None for an entry that reads another entry's cache.  Behind the schedule's entries comes what
+        the model itself keeps per sequence: the token before the next one (int32), where the embedding reads pairs."""
+        needs = [None if e.cache_of is not None else self.layers[e.layer].cache_needs() for e in self.plan.schedule]
+        if self.plan.embedding_pairs is not None:
+            needs.append(CacheNeeds(state_elems=1, state_dtype="int32"))
+        return needs
 
     # ------------------------------------------------------------------ a step
     def hidden(self, token_ids: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         """The residual stream [T, hidden] float32 after the last layer."""
-        x = kernels.embed(self.embedding, token_ids)
+        pairs = self.plan.embedding_pairs
+        if pairs is None:
+            x = kernels.embed(self.embedding, token_ids)
+        else:
+            x = kernels.embed_pairs(self.embedding, self.pair_table, token_ids, ctx.tok_pos, ctx.tok_row, ctx.row_first, ctx.slots,
+                                    ctx.state(len(self.plan.schedule)), pairs.buckets, pairs.mul_prev, pairs.mul_cur)
         if self.embedding_position is not None:
             self.embedding_position.add_to(x, ctx)
         x0 = x.clone() if self._keeps_embedding else None
@@ -97,7 +111,7 @@ class DecoderModel:
         """Bytes of weights a step reads in full: every matrix and vector of every executed layer
         and the head; the embedding table only where it is the head too (a lookup reads a row a token)."""
         seen, total = set(), 0
-        tensors = [self.head] + list(self.final_norm.weights())
+        tensors = [self.head] + list(self.final_norm.weights())      # (the pair table, like the embedding, is read a row a token)
         for entry in self.plan.schedule:
             for part in self.layers[entry.layer].parts():
                 tensors.extend(part.weights())
