@@ -1,5 +1,5 @@
 """config.json contents of the shapes the benchmarks and tests name: the two tiny test
-configurations, the Qwen2.5 sizes and Mebalorn models at the same widths (weights for them are drawn at random)."""
+configurations, the Qwen2.5 sizes and Mebalorn, Kevelorn and Pupidra models at the same widths (weights for them are drawn at random)."""
 from __future__ import annotations
 
 _QWEN2 = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", "torch_dtype": "bfloat16"}
@@ -72,6 +72,38 @@ SHAPES.update({
     "kevelorn-tiny": kevelorn_shape(64, 4, 2, 16, 160, 4, 256, window=40, experts=4),
     "kevelorn-0.5b": kevelorn_shape(896, 14, 2, 64, 4864, 24, 151936),          # the widths of qwen2.5-0.5b
     "kevelorn-7b": kevelorn_shape(3584, 28, 4, 128, 18944, 28, 152064),         # the widths of qwen2.5-7b
+})
+
+
+def pupidra_shape(width: int, heads: int, kv_heads: int, dim: int, ff: int, layers: int, vocab: int, window: int = 1024,
+                  keep_first: int = 64, experts: int = 8, top: int = 2, state: int = 128, buckets: int = 16381) -> dict:
+    """A Pupidra config.json whose layers take these four forms in turn: windowed attention with kept first keys and keys and
+    values of its own, the state-space mixer (twice the width inside, heads of 64, two groups), latent attention (a cached row
+    of at most 256 entries: rank 2 dim or 256 - dim / 2, rotated part dim / 2), and an attention that reads the first form's
+    keys and values.  Every layer has a mixture whose experts and shared expert are a quarter as wide as a dense feed-forward."""
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 2.0}, "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4}}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+           "mask": {"size": window, "keep_first": keep_first}}
+    rot = max(2, dim // 2)
+    rank = min(2 * dim, 256 - rot)
+    lat = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "kv_rank": rank, "scale": (dim + rot) ** -0.5,
+           "rot": {"base": 100000.0, "dims": rot}}
+    p = min(64, 2 * width)
+    ssm = {"heads": 2 * width // p, "vdim": p, "state": state, "groups": 2 if (2 * width // p) % 2 == 0 else 1, "conv": 4,
+           "norm_groups": 2 if (2 * width // p) % 2 == 0 else 1}
+    out = []
+    for i in range(layers):
+        form = i % 4
+        mixer = (att, ssm, lat, {**att, "kv_from": i - 3})[form]
+        out.append({"type": ("attention", "mamba2", "latent_attention", "attention")[form], "mixer": dict(mixer), "mlp": moe})
+    return {"architecture": "Pupidra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+            "embedding": {"bigram": {"buckets": buckets, "mul_prev": 37, "mul_cur": 11}}, "layers": out}
+
+
+SHAPES.update({
+    "pupidra-tiny": pupidra_shape(64, 4, 2, 16, 160, 4, 256, window=40, keep_first=3, experts=4, state=24, buckets=97),
+    "pupidra-0.5b": pupidra_shape(896, 14, 2, 64, 4864, 24, 151936),            # the widths of qwen2.5-0.5b
+    "pupidra-7b": pupidra_shape(3584, 28, 4, 128, 18944, 28, 152064),           # the widths of qwen2.5-7b
 })
 
 

@@ -1,11 +1,13 @@
 """Two designs side by side at equal layer widths: the Mebalorn decoder (layer norm + input convolution, attention
-with mixed heads or a minGRU recurrence, a dense relu^2 feed-forward, both halves in parallel) or the Kevelorn decoder
+with mixed heads or a minGRU recurrence, a dense relu^2 feed-forward, both halves in parallel), the Kevelorn decoder
 (linear attention with fixed or learned decay, windowed softmax attention with an output gate beside it, gated dense
-feed-forwards and mixtures of experts) and the dense Qwen2 decoder, this library's closest other model.  Random weights; prefill and decode throughput of a few layers, and
+feed-forwards and mixtures of experts) or the Pupidra decoder (post-norm layers with layer scale; windowed attention with a
+distance bias and kept first keys, also on another layer's keys and values; latent attention; a state-space mixer; ungated
+mixtures; a bigram embedding) and the dense Qwen2 decoder, this library's closest other model.  Random weights; prefill and decode throughput of a few layers, and
 the kernels of the new design each beside the Qwen2 kernel that does the like job, as fractions of the measured
 copy bandwidth or matrix throughput.
 
-    python -m pico_engine.design_compare [--design mebalorn|kevelorn] [--sizes s,m,l] [--tokens 2048] [--batch 8] [--context 2048] [--output FILE]
+    python -m pico_engine.design_compare [--design mebalorn|kevelorn|pupidra] [--sizes s,m,l] [--tokens 2048] [--batch 8] [--context 2048] [--output FILE]
 """
 from __future__ import annotations
 
@@ -37,11 +39,18 @@ def kevelorn_config(size: str, layers: int | None = None) -> dict:
     return kevelorn_shape(W, H, G, D, F, layers or L, VOCAB)
 
 
-DESIGNS = {"mebalorn": mebalorn_config, "kevelorn": kevelorn_config}
-
-
-def qwen2_config(size: str) -> dict:
+def pupidra_config(size: str, layers: int | None = None) -> dict:
+    from .config.shapes import pupidra_shape
     W, H, G, D, F, L = SIZES[size]
+    return pupidra_shape(W, H, G, D, F, layers or max(L, 4), VOCAB)          # four layers: every kind of mixer once
+
+
+DESIGNS = {"mebalorn": mebalorn_config, "kevelorn": kevelorn_config, "pupidra": pupidra_config}
+
+
+def qwen2_config(size: str, layers: int | None = None) -> dict:
+    W, H, G, D, F, L = SIZES[size]
+    L = layers or L
     return {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", "torch_dtype": "bfloat16",
             "num_hidden_layers": L, "hidden_size": W, "num_attention_heads": H, "num_key_value_heads": G, "head_dim": D,
             "intermediate_size": F, "vocab_size": VOCAB, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
@@ -184,6 +193,93 @@ def kevelorn_kernel_times(eng, size: str, tokens: int, batch: int, context: int,
     B.close_sequences(eng, slots)
 
 
+def pupidra_kernel_times(eng, size: str, tokens: int, batch: int, context: int, entry) -> None:
+    """The kernels that only the Pupidra parts have (or that they use in a new form), each at the sizes of this shape's layers."""
+    W, H, G, D, F, L = SIZES[size]
+    bf = torch.bfloat16
+    out = entry.out
+    layers = eng.model.layers
+    e_att, e_ssm, e_lat, e_read = 0, 1, 2, 3
+    att, ssm, lat = layers[e_att].mixer, layers[e_ssm].mixer, layers[e_lat].mixer
+    moe = layers[e_att].feed_forward
+    sa, ss, sl = att.spec, ssm.spec, lat.spec
+    inner, bc, conv = ssm._sizes()
+    rank, R = sl.kv_rank, sl.rot_dim
+    q_w, dkv_w, _ = lat._widths()
+    state_floats = ssm.matrix_state_elems()
+
+    def attention_calls(ctx, T, label, seen_biased, seen_all, nbytes_biased=None, nbytes_latent=None):
+        kv = ctx.kv(e_att)
+        qkv = torch.randn(T, att.w_in.shape[0], device="cuda").to(bf)
+        how = dict(flops=4.0 * H * D * seen_biased) if nbytes_biased is None else dict(nbytes=nbytes_biased)
+        entry(f"{label} attention (distance bias, window, kept first keys)", device_us(lambda: kernels.attention_headmix(
+            qkv, qkv.shape[1], H, G, D, D, kv.k, kv.v, kv.table, kv.stride, ctx.tok_pos, ctx.tok_row, sa.window, sa.scale, None, None, ctx,
+            slopes=att.slopes, keep_first=sa.keep_first)), **how)
+        kl = ctx.kv(e_lat)
+        ql = torch.randn(T, H * (rank + R), device="cuda").to(bf)
+        how = dict(flops=2.0 * H * (2 * rank + R) * seen_all) if nbytes_latent is None else dict(nbytes=nbytes_latent)
+        entry(f"{label} attention over latent rows", device_us(lambda: kernels.attention_headmix(
+            ql, ql.shape[1], H, 1, rank + R, rank, kl.k, None, kl.table, kl.stride, ctx.tok_pos, ctx.tok_row, None, sl.scale, None, None, ctx,
+            values_in_keys=True)), **how)
+
+    def state_space_calls(ctx, T, B, label):
+        proj = torch.randn(T, ssm.w_in.shape[0], device="cuda").to(bf)
+        state = ctx.state(e_ssm)
+        entry(f"{label} convolution + silu", device_us(lambda: kernels.conv_silu(
+            proj, inner, conv, ssm.conv_w, ssm.conv_b, state, ssm.state_offset + state_floats, ctx.tok_row, ctx.row_first, ctx.row_lens,
+            ctx.slots)), nbytes=T * conv * (2 + 4))
+        xbc = torch.randn(T, conv, device="cuda")
+        us = device_us(lambda: kernels.state_space_scan(xbc, proj, inner + conv, ssm.dt_bias, ssm.a_log, ssm.d_skip, state, ssm.state_offset,
+                                                        ctx.row_first, ctx.row_lens, ctx.slots, ss.n_heads, ss.head_dim, ss.state, ss.n_groups))
+        entry(f"{label} state-space recurrence", us, nbytes=T * (conv + inner) * 4 + 2 * B * state_floats * 4)
+        out[f"{label} state-space recurrence"]["float32_tflops_per_s"] = 4.0 * inner * ss.state * T / us / 1e6
+        y = torch.randn(T, inner, device="cuda")
+        entry(f"{label} gate x output, norm over groups", device_us(lambda: kernels.gate_norm(
+            y, inner // ss.norm_groups, proj, 0, ssm.norm, ss.norm_eps)), nbytes=T * inner * (4 + 2 + 2))
+
+    slot, ctx = _prompt_context(eng, tokens)
+    window, keep = sa.window, sa.keep_first
+    seen_biased = sum(min(p + 1, window + min(keep, max(0, p + 1 - window))) for p in range(tokens))
+    attention_calls(ctx, tokens, "prefill", seen_biased, tokens * (tokens + 1) / 2)
+    kv = ctx.kv(e_att)
+    qkv = torch.randn(tokens, att.w_in.shape[0], device="cuda").to(bf)
+    entry("prefill unit norm of q and k + cache write", device_us(lambda: kernels.rotary_norm_store(
+        qkv, H, G, D, D, None, 0, True, sa.norm_eps, ctx.tok_pos, ctx.tok_row, kv.k, kv.v, kv.table, kv.stride)), nbytes=tokens * (H + 2 * G) * D * 2 * 2)
+    kl = ctx.kv(e_lat)
+    proj = torch.randn(tokens, lat.w_in.shape[0], device="cuda").to(bf)
+    q_abs = torch.randn(H, tokens, rank, device="cuda").to(bf)
+    entry("prefill latent norm + rotation + cache write + query rows", device_us(lambda: kernels.latent_prepare(
+        proj, H, sl.head_dim, R, rank, q_w, lat.dkv_norm, sl.norm_eps, lat.freq, sl.position.dims, q_abs, ctx.tok_pos, ctx.tok_row, kl.k,
+        kl.table, kl.stride)), nbytes=tokens * 2 * (H * (rank + R) * 2 + H * R + 2 * (rank + R)))
+    o = torch.randn(H, tokens, sl.v_head_dim, device="cuda").to(bf)
+    entry("prefill heads x sigmoid gate (head-major in)", device_us(lambda: kernels.head_gate(o, proj, q_w + dkv_w)), nbytes=tokens * H * sl.v_head_dim * 2 * 2)
+    state_space_calls(ctx, tokens, 1, "prefill")
+    x = torch.randn(tokens, W, device="cuda")
+    y = torch.randn(tokens, W, device="cuda")
+    folded = layers[e_att].mixer_scale.times(layers[e_att].mixer_norm.weight)
+    entry("prefill norm x layer scale into the stream", device_us(lambda: kernels.normed_sum_add(x, [y], [folded], 1e-5, 1.0)), nbytes=tokens * W * 4 * 3)
+    E, top = moe.spec.n_experts, moe.spec.top_k
+    entry("prefill router + softmax over all + choice of experts", device_us(lambda: kernels.moe_route_stream(
+        x, None, 0.0, moe.w_router, E, top, moe._extra(), over_all=True, factor=moe.spec.route_scale)), nbytes=tokens * (W * 4 + (E + 1) * 4))
+    I = moe.w_down.shape[1]
+    hid = torch.randn(tokens, I, device="cuda").to(bf)
+    wts = kernels.moe_route_stream(x, None, 0.0, moe.w_router, E, top, moe._extra(), over_all=True, factor=moe.spec.route_scale)
+    entry("prefill relu^2 x expert weight", device_us(lambda: kernels.weighted_act(hid, "relu2", wts, moe.spec.intermediate)), nbytes=tokens * I * 2 * 2)
+    if eng.model.pair_table is not None:
+        ids = torch.randint(0, VOCAB, (tokens,), device="cuda", dtype=torch.int32)
+        prev = torch.zeros(eng.cache.max_seqs + 2, 1, dtype=torch.int32, device="cuda")
+        big = eng.model.plan.embedding_pairs
+        entry("prefill token rows + bigram rows", device_us(lambda: kernels.embed_pairs(
+            eng.model.embedding, eng.model.pair_table, ids, ctx.tok_pos, ctx.tok_row, ctx.row_first, ctx.slots, prev, big.buckets, big.mul_prev,
+            big.mul_cur)), nbytes=tokens * W * (2 + 2 + 4))
+    eng.cache.close(slot)
+    slots, ctx = _decode_context(eng, batch, context)
+    attention_calls(ctx, batch, "decode", 0, 0, nbytes_biased=batch * min(context, window + keep) * 2 * G * D * 2,
+                    nbytes_latent=batch * context * (rank + R) * 2)
+    state_space_calls(ctx, batch, batch, "decode")
+    B.close_sequences(eng, slots)
+
+
 def kernel_times(size: str, tokens: int, batch: int, context: int, peaks: dict, design: str = "mebalorn") -> Dict[str, dict]:
     """Every kernel of the new design beside the like kernel of the Qwen2 decoder: microseconds, the bytes or
     multiply-adds it must move or do, and that as a fraction of the measured peak."""
@@ -204,6 +300,14 @@ def kernel_times(size: str, tokens: int, batch: int, context: int, peaks: dict, 
     # (the kernels of the Kevelorn parts are timed in a model of three layers, which has every kind of part once)
     first = kevelorn_config(size, 3) if design == "kevelorn" else DESIGNS[design](size)
     for design, cfg in ((design, first), ("qwen2", qwen2_config(size))):
+        if design == "pupidra":
+            eng = Engine.from_config(config_from_dict(cfg), seed=1, draw_on="cuda", dtype="bfloat16")
+            eng.ensure_cache(max(tokens, batch * context) + 64 * batch, max(tokens, context), max_seqs=batch + 1)
+            pupidra_kernel_times(eng, size, tokens, batch, context, entry)
+            kernels.check_status(eng.device)
+            del eng
+            torch.cuda.empty_cache()
+            continue
         eng = Engine.from_config(config_from_dict(cfg), seed=1, draw_on="cuda", dtype="bfloat16")
         eng.ensure_cache(max(tokens, batch * context) + 64 * batch, max(tokens, context), max_seqs=batch + 1)
         if design == "kevelorn":
@@ -275,7 +379,8 @@ def throughput(size: str, tokens: int, batch: int, context: int, steps: int = 64
     """Prefill of one prompt and decode of ``batch`` sequences through the engines' own steps, both designs."""
     from .engine.engine import Engine
     out = {}
-    for design, cfg in ((design, DESIGNS[design](size)), ("qwen2", qwen2_config(size))):
+    n_layers = max(SIZES[size][5], 4) if design == "pupidra" else None      # the same number of layers on both sides
+    for design, cfg in ((design, DESIGNS[design](size)), ("qwen2", qwen2_config(size, n_layers))):
         eng = Engine.from_config(config_from_dict(cfg), seed=1, draw_on="cuda", dtype="bfloat16")
         pre = B.prefill_device(eng, tokens)
         dec = B.decode_device(eng, batch, context, steps, 4)
@@ -289,7 +394,8 @@ def throughput(size: str, tokens: int, batch: int, context: int, steps: int = 64
 
 
 def compare(sizes, tokens: int, batch: int, context: int, peaks: dict, design: str = "mebalorn") -> dict:
-    record = {"tokens": tokens, "batch": batch, "context": context, "layers": {s: SIZES[s][5] for s in sizes},
+    record = {"tokens": tokens, "batch": batch, "context": context,
+              "layers": {s: max(SIZES[s][5], 4) if design == "pupidra" else SIZES[s][5] for s in sizes},
               "widths": {s: dict(zip(("width", "heads", "kv_heads", "head_dim", "ff"), SIZES[s][:5])) for s in sizes}, "sizes": {}}
     for s in sizes:
         record["sizes"][s] = {"throughput": throughput(s, tokens, batch, context, design=design),

@@ -52,7 +52,9 @@ def softmax_rows(s, visible):
 
 def embed(tokens, w, big):
     """Token rows plus bigram rows: (previous * mul_prev + current * mul_cur) mod buckets, and row ``buckets`` for the
-    first token of a sequence."""
+    first token of a sequence (``big`` None: token rows alone)."""
+    if big is None:
+        return torch.stack([w["embed"][t] for t in tokens])
     rows = []
     for p, t in enumerate(tokens):
         r = big["buckets"] if p == 0 else (tokens[p - 1] * big["mul_prev"] + t * big["mul_cur"]) % big["buckets"]
@@ -197,9 +199,16 @@ def expert(h, w, p):
     return lin(w[p + "down"], relu2(lin(w[p + "up"], h)))
 
 
+ROUTER_GAPS = None      # a list: every mixture appends, per token, the gap between the logits of its last chosen and first unchosen expert
+
+
 def mixture(h, mlp, w, p):
     r = mlp["router"]
-    scores = torch.softmax(lin(w[p + "router"], h), dim=-1)
+    z = lin(w[p + "router"], h)
+    scores = torch.softmax(z, dim=-1)
+    if ROUTER_GAPS is not None and r["top"] < r["experts"]:
+        ranked = z.sort(dim=-1, descending=True).values
+        ROUTER_GAPS.append((ranked[:, r["top"] - 1] - ranked[:, r["top"]]).detach())
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         chosen = torch.topk(scores[t], r["top"]).indices.tolist()
@@ -221,7 +230,7 @@ def feed_forward(h, mlp, w, p):
 def layer_streams(tokens, cfg, w):
     """The residual stream after every layer, [layers, n, width]."""
     eps = cfg["norm"]["eps"]
-    x = embed(tokens, w, cfg["embedding"]["bigram"])
+    x = embed(tokens, w, (cfg.get("embedding") or {}).get("bigram"))
     kept = {}
     out = []
     for i, layer in enumerate(cfg["layers"]):
