@@ -230,7 +230,8 @@ def pupidra_kernel_times(eng, size: str, tokens: int, batch: int, context: int, 
             ctx.slots)), nbytes=T * conv * (2 + 4))
         xbc = torch.randn(T, conv, device="cuda")
         us = device_us(lambda: kernels.state_space_scan(xbc, proj, inner + conv, ssm.dt_bias, ssm.a_log, ssm.d_skip, state, ssm.state_offset,
-                                                        ctx.row_first, ctx.row_lens, ctx.slots, ss.n_heads, ss.head_dim, ss.state, ss.n_groups))
+                                                        ctx.row_first, ctx.row_lens, ctx.slots, ss.n_heads, ss.head_dim, ss.state, ss.n_groups,
+                                                        chunked=ssm.chunks_pay(ctx.lens)))
         entry(f"{label} state-space recurrence", us, nbytes=T * (conv + inner) * 4 + 2 * B * state_floats * 4)
         out[f"{label} state-space recurrence"]["float32_tflops_per_s"] = 4.0 * inner * ss.state * T / us / 1e6
         y = torch.randn(T, inner, device="cuda")

@@ -1138,6 +1138,14 @@ def state_space_elems(n_heads: int, head_dim: int, state: int) -> int:
     return n_heads * ((state + ns - 1) // ns) * ns * head_dim
 
 
+def state_space_split(state: int) -> int:
+    """Threads that share a column of the state (pe_state_space_split of csrc/state_space.cu gives the same number)."""
+    ns = 1
+    while (state + ns - 1) // ns > 16 and ns < 32:
+        ns *= 2
+    return ns
+
+
 def conv_silu(proj: torch.Tensor, col_offset: int, channels: int, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
               state_offset: int, tok_row: torch.Tensor, row_first: torch.Tensor, row_lens: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
     """silu(bias + sum_j w[:, j] u_(t - taps + 1 + j)) as float32 [T, channels] for the inputs u at columns ``col_offset`` .. of
@@ -1160,10 +1168,12 @@ def conv_silu(proj: torch.Tensor, col_offset: int, channels: int, weight: torch.
 
 def state_space_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_offset: int, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
                      state: torch.Tensor, state_offset: int, row_first: torch.Tensor, row_lens: torch.Tensor, slots: torch.Tensor,
-                     n_heads: int, head_dim: int, n_state: int, n_groups: int) -> torch.Tensor:
+                     n_heads: int, head_dim: int, n_state: int, n_groups: int, chunked: bool = False) -> torch.Tensor:
     """y float32 [T, H * P] of S_t = exp(-exp(A_log) dt) S_(t-1) + dt B_t x_t^T, y_t = S_t^T C_t + D x_t with dt = softplus(raw + bias):
     x | B | C are the columns of ``xbc`` float32 [T, H*P + 2 G N], the raw step sizes columns ``dt_offset`` .. of proj.  The states
-    come from and return to the sequences' float32 state at ``state_offset``."""
+    come from and return to the sequences' float32 state at ``state_offset``.  ``chunked``: prompts, three launches over chunks of 64
+    tokens (every chunk from zero, a carry pass, every chunk from its incoming state) instead of one walk a sequence; both give the
+    same numbers up to float32 rounding."""
     from .library import state_space
     T = xbc.shape[0]
     H, P, N, G = n_heads, head_dim, n_state, n_groups
@@ -1172,11 +1182,15 @@ def state_space_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_offset: int, dt_b
         _need(t, name, None, (H,))
     sp, stride = _state_args(state, state_offset, state_space_elems(H, P, N))
     y = torch.empty(T, H * P, dtype=torch.float32, device=xbc.device)
+    ws = 0
+    if chunked:
+        from .workspace import scratch
+        ws = scratch("state_space_scan", 4 * state_space().pe_state_space_scratch_floats(T, slots.shape[0], H, P, N), xbc.device).data_ptr()
     check(state_space().pe_state_space_scan(xbc.data_ptr(), xbc.shape[1], proj.data_ptr(), _code(proj, "proj"), proj.shape[1], dt_offset,
                                             dt_bias.data_ptr(), _code(dt_bias, "dt_bias"), a_log.data_ptr(), _code(a_log, "a_log"),
                                             d_skip.data_ptr(), _code(d_skip, "d_skip"), sp, stride, row_first.data_ptr(),
-                                            row_lens.data_ptr(), slots.data_ptr(), y.data_ptr(), slots.shape[0], H, P, N, G,
-                                            stream_ptr()), "state_space_scan")
+                                            row_lens.data_ptr(), slots.data_ptr(), y.data_ptr(), T, slots.shape[0], H, P, N, G,
+                                            1 if chunked else 0, ws, stream_ptr()), "state_space_scan", 3 if chunked else 1)
     return y
 
 

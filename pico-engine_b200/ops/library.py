@@ -81,7 +81,7 @@ _GATED_SIGNATURES = {
 
 _STATE_SIGNATURES = {
     "pe_conv_silu": [P, I, I, I, I, I, P, I, P, I, P, LL, P, P, P, P, P, I, I, P],
-    "pe_state_space_scan": [P, I, P, I, I, I, P, I, P, I, P, I, P, LL, P, P, P, P, I, I, I, I, I, P],
+    "pe_state_space_scan": [P, I, P, I, I, I, P, I, P, I, P, I, P, LL, P, P, P, P, I, I, I, I, I, I, I, P, P],
     "pe_gate_norm": [P, I, I, I, P, I, I, I, P, I, F, P, P],
     "pe_latent_prepare": [P, I, I, I, I, I, I, I, I, P, I, F, P, I, P, P, P, P, P, P, I, I, P],
     "pe_head_gate": [P, I, P, I, I, I, I, I, P, P],
@@ -198,6 +198,8 @@ def state_space() -> ctypes.CDLL:
         lib.pe_state_space_split.restype = c_int
         lib.pe_state_space_elems.argtypes = [I, I, I]
         lib.pe_state_space_elems.restype = c_longlong
+        lib.pe_state_space_scratch_floats.argtypes = [I, I, I, I, I]
+        lib.pe_state_space_scratch_floats.restype = c_longlong
         _state = lib
     return _state
 

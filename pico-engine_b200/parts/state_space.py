@@ -72,6 +72,22 @@ class StateSpace(Mixer):
         s = self.spec
         return CacheNeeds(kv=None, state_elems=self.matrix_state_elems() + (s.taps - 1) * self._sizes()[2])
 
+    def chunks_pay(self, lens) -> bool:
+        """Whether a step with these numbers of tokens a row runs its recurrence in chunks.  One walk a sequence takes as long as
+        the longest row, however empty that leaves the GPU; in chunks of 64 every token is walked twice, but all chunks run side
+        by side.  Both are counted in token times a wave of blocks (about two blocks of 256 threads an SM on 148 SMs), the
+        carry pass as one chunk more.  Either way gives the same numbers up to float32 rounding."""
+        longest = max(lens, default=0)
+        if longest <= 64:
+            return False
+        s = self.spec
+        split = kernels.state_space_split(s.state)
+        per = s.n_heads * -(-s.head_dim // min(s.head_dim, 256 // split))     # blocks a sequence or chunk
+        wave = 296
+        walk = longest * -(-sum(1 for n in lens if n > 0) * per // wave)
+        chunks = sum(-(-n // 64) for n in lens)
+        return 64 * (2 * -(-chunks * per // wave) + 1) < walk
+
     def normed_output(self, h, ctx, cache_entry):
         s = self.spec
         inner, bc, conv = self._sizes()
@@ -80,7 +96,8 @@ class StateSpace(Mixer):
         xbc = kernels.conv_silu(proj, inner, conv, self.conv_w, self.conv_b, state, self.state_offset + self.matrix_state_elems(),
                                 ctx.tok_row, ctx.row_first, ctx.row_lens, ctx.slots)
         y = kernels.state_space_scan(xbc, proj, inner + conv, self.dt_bias, self.a_log, self.d_skip, state, self.state_offset,
-                                     ctx.row_first, ctx.row_lens, ctx.slots, s.n_heads, s.head_dim, s.state, s.n_groups)
+                                     ctx.row_first, ctx.row_lens, ctx.slots, s.n_heads, s.head_dim, s.state, s.n_groups,
+                                     chunked=self.chunks_pay(ctx.lens))
         return kernels.gate_norm(y, inner // s.norm_groups, proj, 0, self.norm, s.norm_eps)
 
     def apply(self, h, ctx, entry, cache_entry, owns_cache, out_dtype=None):

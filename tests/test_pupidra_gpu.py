@@ -281,7 +281,7 @@ def test_a_key_from_far_back(dtype, far):
 
 # ------------------------------------------------------------------ the state-space mixer's kernels, alone
 
-def run_state_space(proj, m, conv_w, conv_b, dt_bias, a_log, d_skip, norm_w, eps, dt, lens, cuts):
+def run_state_space(proj, m, conv_w, conv_b, dt_bias, a_log, d_skip, norm_w, eps, dt, lens, cuts, chunked=False):
     """Convolution, recurrence and gated norm on packed sequences of ``lens`` tokens (rows of proj = z | x | B | C | dt), brought
     in steps that cut every sequence at the fractions ``cuts``; returns [T, inner] and the final matrix states."""
     from pico_engine.ops import kernels
@@ -309,7 +309,7 @@ def run_state_space(proj, m, conv_w, conv_b, dt_bias, a_log, d_skip, norm_w, eps
         sl = slots[torch.tensor(rows).cuda()].contiguous()
         p = dev[idx.cuda()].contiguous()
         xbc = kernels.conv_silu(p, inner, conv, cw, cb, state, 5 + elems, tr, rf, rl, sl)
-        y = kernels.state_space_scan(xbc, p, inner + conv, *f32, state, 5, rf, rl, sl, H, P, N, G)
+        y = kernels.state_space_scan(xbc, p, inner + conv, *f32, state, 5, rf, rl, sl, H, P, N, G, chunked=chunked)
         out[idx] = kernels.gate_norm(y, inner // groups, p, 0, nw, eps).float().cpu()
         done = upto
     assert float(state[0].min()) == 3.0 and float(state[B + 1].min()) == 3.0 and float(state[:, :5].min()) == 3.0
@@ -337,11 +337,12 @@ def plain_state_space(proj, m, conv_w, conv_b, dt_bias, a_log, d_skip, norm_w, e
 @pytest.mark.parametrize("H,P,N,G,taps,groups", [(4, 16, 24, 2, 3, 4), (2, 8, 40, 1, 2, 1), (3, 5, 7, 3, 1, 3), (4, 32, 128, 4, 4, 2),
                                                   (2, 64, 16, 2, 4, 1), (1, 40, 200, 1, 5, 8), (6, 24, 64, 3, 4, 2)])
 def test_state_space_kernels(dtype, H, P, N, G, taps, groups):
-    """Sequences of many lengths as one prompt step, in portions, and with the last tokens one by one."""
+    """Sequences of many lengths as one prompt step, in portions, and with the last tokens one by one; a sequence's walk and the
+    three passes over chunks of 64."""
     dt = DTYPES[dtype]
     m = {"heads": H, "vdim": P, "state": N, "groups": G, "conv": taps, "norm_groups": groups}
     g = torch.Generator().manual_seed(H * 1000 + N)
-    lens = [1, 2, 9, 70, 3, 131]
+    lens = [1, 2, 9, 70, 3, 131, 64, 200]
     T, inner, conv = sum(lens), H * P, H * P + 2 * G * N
     r = lambda *s: torch.randn(*s, generator=g)
     rounded = lambda t: t.to(dt).float()
@@ -352,14 +353,16 @@ def test_state_space_kernels(dtype, H, P, N, G, taps, groups):
     want = plain_state_space(proj, *args, lens)
     tol = (3e-5 if dtype == "float32" else 1.5e-2) * max(1.0, float(want.abs().max()))
     for cuts in ((1.0,), (0.4, 0.75, 1.0), (0.97, 0.98, 0.99, 1.0)):
-        got = run_state_space(proj, *args, dt, lens, cuts)
-        assert (got.double() - want).abs().max() < tol, cuts
+        for chunked in (False, True):
+            got = run_state_space(proj, *args, dt, lens, cuts, chunked)
+            assert (got.double() - want).abs().max() < tol, (cuts, chunked)
 
 
-@pytest.mark.parametrize("far", [0, 1, 7, 8, 9, 447])
+@pytest.mark.parametrize("far", [0, 1, 7, 8, 9, 63, 64, 65, 447, 511, 512])
 def test_state_keeps_an_input_from_far_back(far):
     """With a decay of nearly 1 an input whose B matches the last token's C must come through from any distance: the first
-    positions, the borders of the kernel's groups of tokens, hundreds of tokens back, also when the last token comes alone."""
+    positions, the borders of the kernel's groups of tokens and of its chunks, hundreds of tokens back, also when the last token
+    comes alone."""
     m = {"heads": 1, "vdim": 4, "state": 8, "groups": 1, "conv": 1, "norm_groups": 1}
     n, inner, N = 600, 4, 8
     g = torch.Generator().manual_seed(far)
@@ -373,9 +376,9 @@ def test_state_keeps_an_input_from_far_back(far):
     args = (m, ones, zeros, torch.zeros(1), torch.full((1,), -12.0), torch.zeros(1), torch.ones(inner), 1e-5)
     want = plain_state_space(proj, *args, [n])
     assert float(want[-1].abs().min()) > 0.9                      # the norm makes it 1: the far input dominates the last row
-    for cuts in ((1.0,), (0.5, (n - 1) / n, 1.0)):
-        got = run_state_space(proj, *args, torch.float32, [n], cuts)
-        assert (got[-1].double() - want[-1]).abs().max() < 1e-3, (far, cuts)
+    for cuts, chunked in (((1.0,), False), ((1.0,), True), ((0.5, (n - 1) / n, 1.0), False), ((0.3, (n - 1) / n, 1.0), True)):
+        got = run_state_space(proj, *args, torch.float32, [n], cuts, chunked)
+        assert (got[-1].double() - want[-1]).abs().max() < 1e-3, (far, cuts, chunked)
 
 
 # ------------------------------------------------------------------ the router, the experts' hidden units, pairs of tokens
