@@ -55,6 +55,8 @@
 struct AtArgs {
     bf16* out; const int* block_table; int table_stride; const int4* tiles;
     int nh, nkv, window; float scale_log2e;
+    int keep_first;                                // with a window: the first so many keys of a sequence stay visible
+    const float* slopes; float inv_scale;          // [nh] or null: slopes[h] * (query position - key position) is taken off the scaled score
     int pool_rows;                                 // rows of the key (and value) pool seen as a matrix [rows][head size]
 };
 
@@ -207,8 +209,15 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tcgen05_kerne
     const int h = blockIdx.x, kvh = h / (p.nh / p.nkv);
     // the pages the run can see: from the first row's window start to the last row's position, two to a step
     const int first_key = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
-    const int page_lo = first_key / AT_KTILE, page_hi = (pos0 + n - 1) / AT_KTILE;
-    const int n_steps = (page_hi - page_lo + 2) / 2;
+    // (with kept first keys: their pages first, then the window's; where the two meet, all pages from the sequence's start)
+    int page_lo = first_key / AT_KTILE, kept = 0;
+    const int page_hi = (pos0 + n - 1) / AT_KTILE;
+    if (p.window > 0 && p.keep_first > 0) {
+        const int keep_pages = (p.keep_first + AT_KTILE - 1) / AT_KTILE;
+        if (page_lo <= keep_pages) page_lo = 0; else kept = keep_pages;
+    }
+    const int n_pages = kept + page_hi - page_lo + 1, n_steps = (n_pages + 1) / 2;
+    auto page_at = [&](int j) { return j < kept ? j : page_lo + j - kept; };     // the j-th page the run reads, j < n_pages
 
     if (warp == 0) {
         if (lane == 0) {                                            // ---------------- loader
@@ -216,12 +225,12 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tcgen05_kerne
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(at_smem(&q_full)), "r"((unsigned)AT_Q_BYTES) : "memory");
 #pragma unroll
             for (int c = 0; c < AT_PANELS; ++c) at_tma_2d(q_s + c * (AT_QTILE * 128), &map_q, h * AT_HD + 64 * c, tok0, at_smem(&q_full));
-            int page[2] = {table[page_lo], page_lo + 1 <= page_hi ? table[page_lo + 1] : -1};
+            int page[2] = {table[page_at(0)], 1 < n_pages ? table[page_at(1)] : -1};
             for (int it = 0; it < n_steps; ++it) {
                 const int s = it % AT_STAGES;
                 int next[2] = {-1, -1};                             // the step after this one: its entries travel during the wait
-                if (page_lo + 2 * it + 2 <= page_hi) next[0] = table[page_lo + 2 * it + 2];
-                if (page_lo + 2 * it + 3 <= page_hi) next[1] = table[page_lo + 2 * it + 3];
+                if (2 * it + 2 < n_pages) next[0] = table[page_at(2 * it + 2)];
+                if (2 * it + 3 < n_pages) next[1] = table[page_at(2 * it + 3)];
                 if (it >= AT_STAGES && !at_wait(at_smem(&kv_empty[s]), (unsigned)((it / AT_STAGES) - 1) & 1u)) { atomicExch(status, 5); break; }
                 const unsigned bar = at_smem(&kv_full[s]), k_dst = kv_s + s * AT_STAGE_BYTES, v_dst = k_dst + AT_STAGE_BYTES / 2;
                 stage_flags[s] = (page[0] >= 0 ? 1u : 0u) | (page[1] >= 0 ? 2u : 0u);
@@ -292,6 +301,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tcgen05_kerne
         const unsigned o_addr = lane_addr + AT_O_COL + g * (AT_HD / 2);
         const unsigned pair = at_smem(&pair_bar[quarter]);
         float m_run = -INFINITY, l_run = 0.f;
+        const float slope = p.slopes ? p.slopes[h] * p.inv_scale : 0.f;     // in units of the unscaled score
         bool ok = true;
         int it = 0, met = 0;                                        // met: how often the row's two threads have met
         // tell the other half `mine`, learn what it tells
@@ -311,7 +321,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tcgen05_kerne
             const bool there = (stage_flags[st] >> g) & 1u;
             if (!at_wait_warp(at_smem(&s_full[b]), (unsigned)(it >> 1) & 1u)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int key0 = (page_lo + 2 * it + g) * AT_KTILE;
+            const int key0 = page_at(2 * it + g) * AT_KTILE;
             unsigned raw[AT_KTILE];
             at_ld32_start(lane_addr + b * (2 * AT_KTILE) + g * AT_KTILE, raw);
             at_ld32_start(lane_addr + b * (2 * AT_KTILE) + g * AT_KTILE + 32, raw + 32);
@@ -324,18 +334,27 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tcgen05_kerne
             float s[AT_KTILE];
 #pragma unroll
             for (int c = 0; c < AT_KTILE; ++c) s[c] = __uint_as_float(raw[c]);
-            const bool whole = there && key0 + AT_KTILE - 1 <= p_r && (p.window <= 0 || key0 > p_r - p.window);
+            const bool whole = there && key0 + AT_KTILE - 1 <= p_r &&
+                               (p.window <= 0 || key0 > p_r - p.window || key0 + AT_KTILE - 1 < p.keep_first);
             if (!whole) {
 #pragma unroll
                 for (int c = 0; c < AT_KTILE; ++c) {
                     const int key = key0 + c;
-                    if (!there || key > p_r || (p.window > 0 && key <= p_r - p.window)) s[c] = -INFINITY;
+                    if (!there || key > p_r || (p.window > 0 && key <= p_r - p.window && key >= p.keep_first)) s[c] = -INFINITY;
                 }
+            }
+            // the distance's share of the score, slope * (key - row): the part that grows along the page is added here, the
+            // page's own part (`base`, one number a thread) joins the maximum and the exponent's offset
+            float base = 0.f;
+            if (p.slopes) {
+                base = slope * (float)(key0 - p_r);
+#pragma unroll
+                for (int c = 0; c < AT_KTILE; ++c) s[c] = fmaf(slope, (float)c, s[c]);
             }
             float mx[4] = {s[0], s[1], s[2], s[3]};                 // four chains: a warp has little else to hide their latency
 #pragma unroll
             for (int c = 4; c < AT_KTILE; ++c) mx[c & 3] = fmaxf(mx[c & 3], s[c]);
-            const float m_mine = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            const float m_mine = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) + base;
             float m_theirs;
             if (!swap(m_mine, m_theirs)) { ok = false; break; }
             // The reference point of the exponentials follows the row's maximum only when that has grown by more than
@@ -349,9 +368,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tcgen05_kerne
             m_run = m_new;
             float sum[4] = {0.f, 0.f, 0.f, 0.f};
             unsigned packed[AT_KTILE / 2];
+            const float off = fmaf(base, p.scale_log2e, -m_use);
 #pragma unroll
             for (int c = 0; c < AT_KTILE; c += 2) {
-                const float e0 = at_exp2(fmaf(s[c], p.scale_log2e, -m_use)), e1 = at_exp2(fmaf(s[c + 1], p.scale_log2e, -m_use));
+                const float e0 = at_exp2(fmaf(s[c], p.scale_log2e, off)), e1 = at_exp2(fmaf(s[c + 1], p.scale_log2e, off));
                 sum[c & 3] += e0; sum[(c + 1) & 3] += e1;
                 packed[c >> 1] = at_pack(e0, e1);
             }
@@ -460,7 +480,7 @@ extern "C" int pe_attention_prefill_tcgen05_ctas_per_sm() {
 extern "C" int pe_attention_prefill_tcgen05(const void* q, int q_stride, void* out, const void* k_pool, const void* v_pool,
                                             long long pool_pages, const int* block_table, int table_stride, const void* tiles,
                                             int n_tiles, int n_tokens, int nh, int nkv, int hd, int window, float scale,
-                                            int* status, void* stream) {
+                                            int keep_first, const float* slopes, int* status, void* stream) {
     if (n_tiles <= 0) return 0;
     if (hd != AT_HD || nkv <= 0 || nh % nkv || n_tiles > 65535 || q_stride % 8 || !(scale > 0.f) || !status) return PE_ERR_UNSUPPORTED;
     if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out | (uintptr_t)tiles) & 15) return PE_ERR_UNSUPPORTED;
@@ -475,6 +495,7 @@ extern "C" int pe_attention_prefill_tcgen05(const void* q, int q_stride, void* o
     AtArgs p = {};
     p.out = (bf16*)out; p.block_table = block_table; p.table_stride = table_stride; p.tiles = (const int4*)tiles;
     p.nh = nh; p.nkv = nkv; p.window = window; p.scale_log2e = scale * 1.4426950408889634f;
+    p.keep_first = window > 0 && keep_first > 0 ? keep_first : 0; p.slopes = slopes; p.inv_scale = 1.0f / scale;
     p.pool_rows = (int)(pool_pages * nkv * AT_KTILE);
     const size_t smem = AT_SMEM_BYTES;
     static bool attr_set = false;
@@ -491,7 +512,7 @@ extern "C" int pe_attention_prefill_tcgen05(const void* q, int q_stride, void* o
 extern "C" int pe_attention_prefill_tcgen05_tile() { return 0; }
 extern "C" int pe_attention_prefill_tcgen05_ctas_per_sm() { return 0; }
 extern "C" int pe_attention_prefill_tcgen05(const void*, int, void*, const void*, const void*, long long, const int*, int, const void*,
-                                            int, int, int, int, int, int, float, int*, void*) {
+                                            int, int, int, int, int, int, float, int, const float*, int*, void*) {
     return PE_ERR_UNSUPPORTED;
 }
 

@@ -369,15 +369,18 @@ def attention_prefill_tcgen05_takes(head_dim: int, scale: float) -> bool:
 def attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: int, head_dim: int,
                               k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, table_stride: int,
                               tiles: torch.Tensor, n_tokens: int, window: Optional[int], scale: float,
-                              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                              out: Optional[torch.Tensor] = None, keep_first: int = 0,
+                              slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The same on the tcgen05 tensor cores, for head sizes 64 and 128 and runs ``tiles`` of at most
-    128 tokens.  ``q`` is a view of ``n_tokens`` rows, ``q_stride`` elements apart."""
+    128 tokens.  ``q`` is a view of ``n_tokens`` rows, ``q_stride`` elements apart.  ``keep_first``: with a window, the first so
+    many keys of a sequence stay visible.  ``slopes`` float32 [heads]: slope_h * (i - j) is taken off the score of query i and
+    key j."""
     from .library import for_head_dim
     out = _prefill_args(q, n_heads, n_kv_heads, head_dim, k_pool, v_pool, block_table, tiles, n_tokens, out)
     check(for_head_dim(head_dim).pe_attention_prefill_tcgen05(
         q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0], block_table.data_ptr(),
         table_stride, tiles.data_ptr(), tiles.shape[0], n_tokens, n_heads, n_kv_heads, head_dim, window or 0,
-        float(scale), status_ptr(q.device), stream_ptr()), "attention_prefill_tcgen05")
+        float(scale), keep_first if window else 0, _ptr(slopes), status_ptr(q.device), stream_ptr()), "attention_prefill_tcgen05")
     return out
 
 
@@ -856,6 +859,16 @@ def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, h
         _need(sink, "sink", None, (n_heads,))
     if mix is not None:
         _need(mix, "mix", None, (n_heads, n_heads))
+    if (q.dtype == torch.bfloat16 and not ctx.one_token_each and sink is None and mix is None and not values_in_keys
+            and head_dim == v_head_dim and attention_prefill_tcgen05_takes(head_dim, scale) and q_stride % 8 == 0
+            and HEADMIX_TENSOR_CORES == "1"):
+        # one weight a (query, key) and equal sizes of 64 or 128: the tcgen05 kernel of the plain attention, which takes the
+        # distance's share of the score and the kept first keys
+        tiles = ctx.scratch.get("prefill_tiles_128")
+        if tiles is None:
+            tiles = ctx.scratch["prefill_tiles_128"] = prefill_tiles(ctx.lens, ctx.starts, q.device, PREFILL_TILE_TCGEN05)
+        return attention_prefill_tcgen05(q, q_stride, n_heads, n_kv, head_dim, k_pool, v_pool, block_table, table_stride, tiles, T,
+                                         window, scale, keep_first=keep_first, slopes=slopes)
     lib = mixers()
     tiles, n_runs = None, 0
     if not ctx.one_token_each:

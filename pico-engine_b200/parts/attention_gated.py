@@ -91,6 +91,9 @@ class GatedAttention(Mixer):
         gated()                                            # build or load this part's kernels now, loudly
         if not self.plain_kernels:
             mixers()
+            if (self.dtype == torch.bfloat16 and self.spec.head_dim == self.spec.v_head_dim
+                    and kernels.attention_prefill_tcgen05_takes(self.spec.head_dim, self.spec.scale)):
+                for_head_dim(self.spec.head_dim)           # prompts run on the tcgen05 kernel
         elif self.dtype == torch.bfloat16:
             for_head_dim(self.spec.head_dim)
         if isinstance(self.spec.position, RotaryPairsSpec):

@@ -232,7 +232,8 @@ def test_biased_attention_kernel(dtype, H, G, D, Dv, window, keep):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,G,D,Dv,window,keep", [(6, 2, 32, 16, 40, 5), (3, 1, 24, 12, 2, 1), (8, 1, 64, 64, 130, 70), (2, 2, 16, 16, 64, 64)])
+@pytest.mark.parametrize("H,G,D,Dv,window,keep", [(6, 2, 32, 16, 40, 5), (3, 1, 24, 12, 2, 1), (8, 1, 64, 64, 130, 70), (2, 2, 16, 16, 64, 64),
+                                                  (2, 1, 64, 64, 66, 3), (2, 2, 128, 128, 40, 65)])
 def test_window_and_kept_edges_in_prompt_and_decoding(dtype, H, G, D, Dv, window, keep):
     """One key is made to dominate for the queries that follow it.  A key behind the kept ones must be seen by the query
     window - 1 places after it and not by the next one; the last kept key must be seen from everywhere and the first key
@@ -252,6 +253,23 @@ def test_window_and_kept_edges_in_prompt_and_decoding(dtype, H, G, D, Dv, window
             for p in range(key_at + 1, n):
                 seen = p - key_at < window or key_at < keep
                 assert ((got[p] - 100.0).abs().max() < 1.0) == seen, (key_at, p, len(spans), got[p].abs().max())
+
+
+@pytest.mark.parametrize("H,G,D,window,keep", [(4, 2, 64, 100, 70), (2, 1, 128, 65, 3), (2, 2, 64, 64, 0), (3, 1, 64, None, 0),
+                                               (2, 2, 128, 200, 128), (2, 1, 64, 300, 1)])
+def test_long_prompts_in_bfloat16_at_head_sizes_of_the_tensor_memory_kernel(H, G, D, window, keep):
+    """Prompts long enough that the pages of the kept first keys and the pages of the window lie apart, whole and in portions
+    that begin and end off the borders of pages and of the kernel's runs of tokens."""
+    dt, n = torch.bfloat16, 900
+    g = torch.Generator().manual_seed(H * 100 + D + (window or 0))
+    q, k, v = ((torch.randn(n, h, D, generator=g)).to(dt).float() for h in (H, G, G))
+    scale = 0.7 * D ** -0.5
+    want = plain.biased_attention(q.double(), k.double(), v.double(), scale, window, keep)
+    kp, table = paged(k, dt)
+    vp, _ = paged(v, dt)
+    for spans in ([(0, n)], [(0, 130), (130, 133), (133, 517), (517, n)]):
+        got = run_attention(q, kp, vp, table, dt, spans, window, keep, scale, plain.distance_slopes(H), D)
+        assert (got.double() - want).abs().max() < 2e-2 * max(1.0, float(want.abs().max())), spans[:2]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
