@@ -139,10 +139,12 @@ __device__ __forceinline__ float ad_ex2(float x) {          // 2^x; 2^-inf = 0
 
 // One tile of 16 keys against the warp's 16 query rows.  kt, vt: shared-memory addresses of the
 // tile's first key and value row; key0: position of that key.  At least one key of the tile is
-// visible (lo <= key <= pos), so every row's running max is finite after it.
+// visible (lo <= key <= pos, or key < keep and key <= pos), so every row's running max is finite after it.
+// biased: bias[r] * (pos - key) is taken off the unscaled scores of row g + 8 r (a distance slope over the score's scale).
 __device__ __forceinline__ void ad_consume(float (&acc)[AD_NCHUNK][4][4], float (&m_run)[2], float (&l_run)[2],
                                            const uint4 (&qf)[AD_NCHUNK][2], unsigned kt, unsigned vt, int key0, int lo,
-                                           int pos, float scale_log2e, int g, int t) {
+                                           int pos, float scale_log2e, int g, int t, int keep, bool biased,
+                                           const float (&bias)[2]) {
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     float sc[2][4];
 #pragma unroll
@@ -157,13 +159,19 @@ __device__ __forceinline__ void ad_consume(float (&acc)[AD_NCHUNK][4][4], float 
         }
     }
     // sc[j][e]: row (e & 2 ? g + 8 : g), key key0 + j*8 + 2t + (e & 1)
+    if (biased) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sc[j][e] = fmaf(-bias[e >> 1], (float)(pos - (key0 + j * 8 + 2 * t + (e & 1))), sc[j][e]);
+    }
     if (key0 < lo || key0 + 15 > pos) {                      // a tile on the edge of what is visible
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = key0 + j * 8 + 2 * t + (e & 1);
-                if (key < lo || key > pos) sc[j][e] = -INFINITY;
+                if ((key < lo && key >= keep) || key > pos) sc[j][e] = -INFINITY;
             }
     }
     float tmax[2];
@@ -216,7 +224,7 @@ __global__ void __launch_bounds__(32 * (AD_WARPS + 1), AD_CTAS(AD_WARPS)) attent
     const bf16* q, int q_stride, const bf16* k_pool, const bf16* v_pool,
     const int* block_table, int table_stride, const int* tok_pos,
     const int* tok_row, int nh, int nkv, int window, float scale_log2e, int n_splits, int stages,
-    int* status, bf16* out) {
+    int* status, bf16* out, int keep_first, const float* slopes) {
     constexpr int AD_GROUPS = AD_WARPS / 4, AD_THREADS = 32 * (AD_WARPS + 1);
     extern __shared__ __align__(128) unsigned char ad_smem[];   // result rows, then the ring (later: the warps' partial results)
     __shared__ __align__(8) unsigned long long bars[2 * AD_MAX_STAGES + 1];
@@ -233,10 +241,15 @@ __global__ void __launch_bounds__(32 * (AD_WARPS + 1), AD_CTAS(AD_WARPS)) attent
     const int pos = tok_pos[tok];
     const int* table = block_table + (size_t)tok_row[tok] * table_stride;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int first_page = lo / PE_PAGE, last_page = pos / PE_PAGE;
-    const int per_split = (last_page - first_page + n_splits) / n_splits;          // ceil(pages / n_splits)
-    const int p0 = first_page + split * per_split;
-    int n_mine = max(0, min(p0 + per_split, last_page + 1) - p0);
+    // The pages a token reads, in the order they are visited: those of the sequence's first keep_first keys where the window
+    // has left them behind, then the window's.  Entry v of that list is page v (v < kept_pages) or first_page + v - kept_pages.
+    int first_page = lo / PE_PAGE, kept_pages = (window > 0 && keep_first > 0) ? (keep_first + PE_PAGE - 1) / PE_PAGE : 0;
+    if (first_page <= kept_pages) { first_page = 0; kept_pages = 0; }             // the window reaches the kept pages: one run from page 0
+    const int last_page = pos / PE_PAGE, n_pages = kept_pages + last_page - first_page + 1;
+    const int skipped = first_page - kept_pages;                                   // pages between the kept ones and the window's
+    const int per_split = (n_pages + n_splits - 1) / n_splits;
+    const int p0 = split * per_split;
+    int n_mine = max(0, min(p0 + per_split, n_pages) - p0);
     if (n_mine > stages && stages % AD_GROUPS) {             // a ring the host must not give (see how the warps share the pages)
         if (threadIdx.x == 0) atomicExch(status, 3);
         n_mine = 0;
@@ -280,7 +293,7 @@ __global__ void __launch_bounds__(32 * (AD_WARPS + 1), AD_CTAS(AD_WARPS)) attent
         bool alive = true;
         for (int base = 0; base < n_mine && alive; base += 32) {
             __syncwarp();
-            if (base + lane < n_mine) page_list[lane] = table[p0 + base + lane];
+            if (base + lane < n_mine) { const int v = p0 + base + lane; page_list[lane] = table[v < kept_pages ? v : v + skipped]; }
             __syncwarp();
             if (lane == 0) {
                 int s = base % stages, round = base / stages;
@@ -322,6 +335,13 @@ __global__ void __launch_bounds__(32 * (AD_WARPS + 1), AD_CTAS(AD_WARPS)) attent
             qf[c][1] = (cin && r_hi < G) ? ad_ld16(qp + (size_t)(kvh * G + r_hi) * AD_HD) : zero;
         }
         const int grp = warp >> 2, first_key = (warp & 3) * 16;
+        const bool biased = slopes != nullptr;
+        float bias[2] = {0.f, 0.f};                             // slope over scale, in the unscaled scores' units
+        if (biased) {
+            const float unit = 1.4426950408889634f / scale_log2e;
+            if (r_lo < G) bias[0] = slopes[kvh * G + r_lo] * unit;
+            if (r_hi < G) bias[1] = slopes[kvh * G + r_hi] * unit;
+        }
         const bool wraps = n_mine > stages;
         bool dead = false;
         int s = grp % stages, round = grp / stages;
@@ -330,8 +350,8 @@ __global__ void __launch_bounds__(32 * (AD_WARPS + 1), AD_CTAS(AD_WARPS)) attent
                 dead = true;
                 if (lane == 0) atomicExch(status, 1);
             }
-            const int key0 = (p0 + i) * PE_PAGE + first_key;
-            if (!dead && key0 <= pos && key0 + 16 > lo && page_ok[s]) {
+            const int key0 = (p0 + i < kept_pages ? p0 + i : p0 + i + skipped) * PE_PAGE + first_key;
+            if (!dead && key0 <= pos && (key0 + 16 > lo || key0 < keep_first) && page_ok[s]) {
                 const unsigned kt = ring0 + s * AD_STAGE_BYTES + (unsigned)(first_key * AD_HD * 2), vt = kt + AD_KV_BYTES;
                 if (pos < key0 + 16) {
                     // The newest token's row: the page was copied while the kernel that writes this row may still
@@ -345,7 +365,7 @@ __global__ void __launch_bounds__(32 * (AD_WARPS + 1), AD_CTAS(AD_WARPS)) attent
                     }
                     __syncwarp();
                 }
-                ad_consume(acc, m_run, l_run, qf, kt, vt, key0, lo, pos, scale_log2e, g, t);
+                ad_consume(acc, m_run, l_run, qf, kt, vt, key0, lo, pos, scale_log2e, g, t, keep_first, biased, bias);
             }
             if (wraps) {                                     // a stage that is used again: tell the producer it is free
                 __syncwarp();
@@ -529,7 +549,8 @@ struct AdVariant {
 
     static int launch(dim3 grid, int n_splits, int stages, cudaStream_t stream, const bf16* q, int q_stride, const bf16* k_pool,
                       const bf16* v_pool, const int* block_table, int table_stride, const int* tok_pos, const int* tok_row,
-                      int nh, int nkv, int window, float scale_log2e, int* status, bf16* out, bool early) {
+                      int nh, int nkv, int window, float scale_log2e, int* status, bf16* out, bool early, int keep_first,
+                      const float* slopes) {
         const size_t smem = smem_bytes(stages);
         { const int e = allow_smem(smem); if (e) return e; }
         cudaLaunchConfig_t cfg = {};
@@ -552,7 +573,7 @@ struct AdVariant {
         cfg.attrs = attr;
         cfg.numAttrs = n_attr;
         PE_TRY(cudaLaunchKernelEx(&cfg, attention_decode_kernel<WARPS>, q, q_stride, k_pool, v_pool, block_table, table_stride,
-                                  tok_pos, tok_row, nh, nkv, window, scale_log2e, n_splits, stages, status, out));
+                                  tok_pos, tok_row, nh, nkv, window, scale_log2e, n_splits, stages, status, out, keep_first, slopes));
         PE_LAUNCH_CHECK();
         return 0;
     }
@@ -591,12 +612,15 @@ extern "C" int pe_attention_decode_splits(int T, int nh, int nkv, int max_contex
 extern "C" int pe_attention_decode(const void* q, int q_stride, void* out, const void* k_pool, const void* v_pool,
                                    const int* block_table, int table_stride, const int* tok_pos, const int* tok_row,
                                    int T, int nh, int nkv, int hd, int window, float scale, int max_context,
-                                   int early_pages, int* status, void* stream) {
+                                   int early_pages, int* status, void* stream, int keep_first, const float* slopes) {
+    // keep_first: with a window, a sequence's first so many keys stay visible.  slopes [nh] float32 (or null):
+    // slope_h * (position - key) is taken off the scaled score.
     // early_pages 1: the kernel may start while the kernels before it in the stream still run, and copies cache pages
     // at once; those kernels (the one before it, and the one before that, which it can overlap too) must then have
     // written no cache row but each token's own (which is fetched again after the wait).  0: it starts when they have ended.
     if (T <= 0) return 0;
     if (hd != AD_HD || nkv <= 0 || nh % nkv || max_context <= 0 || q_stride % 8 || T > 65535 || !status) return PE_ERR_UNSUPPORTED;
+    if (keep_first < 0 || (slopes && !(scale > 0.f))) return PE_ERR_UNSUPPORTED;
     if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) return PE_ERR_UNSUPPORTED;
     const int G = nh / nkv;
     if ((long long)nkv * ((G + 15) / 16) > 65535) return PE_ERR_UNSUPPORTED;
@@ -609,9 +633,9 @@ extern "C" int pe_attention_decode(const void* q, int q_stride, void* out, const
         if (wide)
             return AdVariant<16>::launch(grid, n_splits, stages, (cudaStream_t)stream, (const bf16*)q, q_stride, (const bf16*)k_pool,
                                          (const bf16*)v_pool, block_table, table_stride, tok_pos, tok_row, nh, nkv, window,
-                                         scale_log2e, status, (bf16*)out, early_pages != 0);
+                                         scale_log2e, status, (bf16*)out, early_pages != 0, keep_first, slopes);
     }
     return AdVariant<8>::launch(grid, n_splits, stages, (cudaStream_t)stream, (const bf16*)q, q_stride, (const bf16*)k_pool,
                                 (const bf16*)v_pool, block_table, table_stride, tok_pos, tok_row, nh, nkv, window, scale_log2e,
-                                status, (bf16*)out, early_pages != 0);
+                                status, (bf16*)out, early_pages != 0, keep_first, slopes);
 }

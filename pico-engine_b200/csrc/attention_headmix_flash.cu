@@ -31,8 +31,9 @@ struct FlashMixArgs {
     const int* tiles;                         // prompt: runs of at most 64 tokens (row, first token, tokens, first position); null: single tokens
     int H, G, D, Dv, window; float scale;
     int splits, cg, ngroups;                  // ranges of keys; value heads a block; groups of value heads
-    const float* slopes; int keep_first; int v_ld;   // slope_h * (i - j) is taken off a score (null: nothing); the first keep_first keys stay
-                                                     // visible behind the window; a value row has v_ld entries of which the first Dv are read
+    const float* slopes; int keep_first; int v_ld; int v_in_k;   // slope_h * (i - j) is taken off a score (null: nothing); the first keep_first keys stay
+                                                     // visible behind the window; a value row has v_ld entries of which the first Dv are read;
+                                                     // v_in_k: the values are the front of the one key head's rows and are read from K's copy
     float* pm; float* pl; float* po;          // [T][splits][H], [T][splits][H], [T][splits][H][G][Dv]
 };
 
@@ -67,17 +68,22 @@ __device__ __forceinline__ uint32_t fx_pack(float lo, float hi) {
 }
 
 // DKM: most 16-wide steps of the head size; NVM: most 8-wide value tiles a block accumulates (cg * Dv / 8).
-template <int DKM, int NVM>
+// SUB (single tokens whose query heads of a key/value head fill one warp's 16 rows): every warp takes the same rows and a
+// quarter of each page's keys (16), and leaves a partial result of its own, as if the range were cut in four once more.
+template <int DKM, int NVM, bool SUB>
 __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) flashmix_kernel(FlashMixArgs a) {
+    constexpr int NT = SUB ? 2 : 8;                           // tiles of 8 keys a warp takes of a page
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) unsigned char fx_smem[];
     const int H = a.H, G = a.G, D = a.D, Dv = a.Dv, per_kv = H / G;
     const int kp = D + FX_PAD, vp = Dv + FX_PAD;
-    const size_t stage_elems = (size_t)PE_PAGE * kp + (size_t)a.cg * PE_PAGE * vp;      // a stage: K [64][kp], V [cg][64][vp]
+    const int vs_ld = a.v_in_k ? kp : vp;                     // entries between two value rows in a stage
+    const size_t stage_elems = (size_t)PE_PAGE * kp + (a.v_in_k ? 0 : (size_t)a.cg * PE_PAGE * vp);      // a stage: K [64][kp], V [cg][64][vp]
     bf16* stages = reinterpret_cast<bf16*>(fx_smem);          // two stages: the next page is copied while this one is used
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, split = blockIdx.z;
     const bool prompt = a.tiles != nullptr;
+    const int koff = SUB ? warp * 16 : 0;                     // the warp's first key within a page
 
     // what the block and this warp's 16 rows stand for
     int seq, p_first, p_last, kvh, grp;
@@ -100,7 +106,7 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
         seq = a.tok_row[t]; p_first = p_last = a.tok_pos[t];
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
-            const int i = warp * 16 + (lane >> 2) + x * 8;
+            const int i = (SUB ? 0 : warp * 16) + (lane >> 2) + x * 8;
             live[x] = i < per_kv; tok[x] = t; head[x] = kvh * per_kv + i; qpos[x] = p_first;
         }
     }
@@ -139,7 +145,7 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
         for (int x = 0; x < 2; ++x) slope2[x] = live[x] ? a.slopes[head[x]] * 1.4426950408889634f : 0.f;
     }
     const int q_first = prompt ? a.tiles[4 * blockIdx.x + 3] + warp * 16 : p_first;      // the earliest position among this warp's rows
-    const bool warp_live = prompt ? (warp * 16 < a.tiles[4 * blockIdx.x + 2]) : (warp * 16 < per_kv);
+    const bool warp_live = prompt ? (warp * 16 < a.tiles[4 * blockIdx.x + 2]) : (SUB || warp * 16 < per_kv);
 
     // Copies of one page into a stage.  The page's keys of one key/value head are one contiguous piece of the pool, and so are
     // its values of the group's heads; both go to padded rows in 16-byte units.  A thread's units are `FX_THREADS` apart: their
@@ -159,7 +165,7 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
             if (c >= per) { c -= per; ++r; }
         }
         const bf16* vsrc = a.v_pool + (((size_t)max(page, 0) * G + c_lo) * PE_PAGE) * a.v_ld;
-        for (int r = v_r0, c = v_c0; r < c_n * PE_PAGE;) {
+        for (int r = v_r0, c = v_c0; !a.v_in_k && r < c_n * PE_PAGE;) {
             fx_cp16(vs + (size_t)r * vp + c * 8, vsrc + (size_t)r * a.v_ld + c * 8, (r & (PE_PAGE - 1)) < valid ? 16 : 0);
             r += v_dr; c += v_dc;
             if (c >= perv) { c -= perv; ++r; }
@@ -168,7 +174,7 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
     };
     // where value tile n of this block lies in a stage's V (head n / nvt, columns 8 (n % nvt) ..): a table, not divisions in the loop
     __shared__ int v_off[32];
-    if (tid < 32) v_off[tid] = tid < nv ? (tid / nvt) * PE_PAGE * vp + (tid % nvt) * 8 : 0;
+    if (tid < 32) v_off[tid] = tid < nv ? (tid / nvt) * PE_PAGE * vs_ld + (tid % nvt) * 8 : 0;
     __syncthreads();
     if (b_begin < b_end) copy_page(page_start(b_begin), 0);
     int stage = 0;
@@ -180,18 +186,18 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
         else fx_wait<0>();
         __syncthreads();                                      // this page's copies of all threads have landed
         const bf16* k_s = stages + stage * stage_elems;
-        const bf16* v_lane = k_s + (size_t)PE_PAGE * kp + (lane & 15) * vp;      // this lane's row of a 16-key step of V
-        const bf16* k_lane = k_s + (size_t)(lane & 7) * kp + ((lane >> 3) & 1) * 8;
+        const bf16* v_lane = k_s + (a.v_in_k ? 0 : (size_t)PE_PAGE * kp) + (koff + (lane & 15)) * vs_ld;      // this lane's row of a 16-key step of V
+        const bf16* k_lane = k_s + (size_t)(koff + (lane & 7)) * kp + ((lane >> 3) & 1) * 8;
         if (warp_live) {
-        // S = Q K^T: 8 tiles of 8 keys
-        float s[8][4];
+        // S = Q K^T: NT tiles of 8 keys
+        float s[NT][4];
 #pragma unroll
-        for (int n = 0; n < 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+        for (int n = 0; n < NT; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
 #pragma unroll
         for (int kk = 0; kk < DKM; ++kk) {
             if (kk < dk) {
 #pragma unroll
-                for (int n = 0; n < 8; ++n) {
+                for (int n = 0; n < NT; ++n) {
                     uint32_t bfr[2];
                     fx_ldsm_x2(bfr, k_lane + n * 8 * kp + kk * 16);
                     fx_mma(s[n], qf[kk], bfr);
@@ -203,16 +209,16 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
         if (valid == PE_PAGE && a.window <= 0 && !a.slopes && kb + PE_PAGE - 1 <= q_first) {
             // every key of the page is seen by every row of this warp: nothing to mask
 #pragma unroll
-            for (int n = 0; n < 8; ++n) {
+            for (int n = 0; n < NT; ++n) {
 #pragma unroll
                 for (int x = 0; x < 4; ++x) { s[n][x] *= sl2; mx[x >> 1] = fmaxf(mx[x >> 1], s[n][x]); }
             }
         } else {
 #pragma unroll
-            for (int n = 0; n < 8; ++n) {
+            for (int n = 0; n < NT; ++n) {
 #pragma unroll
                 for (int x = 0; x < 4; ++x) {
-                    const int rr = x >> 1, j = n * 8 + (lane & 3) * 2 + (x & 1), key = kb + j;
+                    const int rr = x >> 1, j = koff + n * 8 + (lane & 3) * 2 + (x & 1), key = kb + j;
                     const bool seen = live[rr] && j < valid && key <= qpos[rr] &&
                                       (a.window <= 0 || qpos[rr] - key < a.window || key < a.keep_first);
                     s[n][x] = seen ? s[n][x] * sl2 - slope2[rr] * (float)(qpos[rr] - key) : -INFINITY;
@@ -232,7 +238,7 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
         }
         const float m0 = m[0] > -INFINITY ? m[0] : 0.f, m1 = m[1] > -INFINITY ? m[1] : 0.f;     // (a row that has seen nothing: exp2(-inf - 0) = 0)
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
+        for (int n = 0; n < NT; ++n) {
             s[n][0] = fx_exp2(s[n][0] - m0); s[n][1] = fx_exp2(s[n][1] - m0);
             s[n][2] = fx_exp2(s[n][2] - m1); s[n][3] = fx_exp2(s[n][3] - m1);
             l[0] += s[n][0] + s[n][1];
@@ -244,14 +250,14 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
         }
         // O' += P V for every value head of the group
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
+        for (int ks = 0; ks < NT / 2; ++ks) {
             uint32_t pf[4] = {fx_pack(s[2 * ks][0], s[2 * ks][1]), fx_pack(s[2 * ks][2], s[2 * ks][3]),
                               fx_pack(s[2 * ks + 1][0], s[2 * ks + 1][1]), fx_pack(s[2 * ks + 1][2], s[2 * ks + 1][3])};
 #pragma unroll
             for (int n = 0; n < NVM; ++n) {
                 if (n < nv) {
                     uint32_t bfr[2];
-                    fx_ldsm_x2_trans(bfr, v_lane + v_off[n] + ks * 16 * vp);
+                    fx_ldsm_x2_trans(bfr, v_lane + v_off[n] + ks * 16 * vs_ld);
                     fx_mma(o[n], pf, bfr);
                 }
             }
@@ -269,7 +275,7 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
         if (!live[rr]) continue;
-        const size_t at = ((size_t)tok[rr] * a.splits + split) * H + head[rr];
+        const size_t at = ((size_t)tok[rr] * (SUB ? 4 * a.splits : a.splits) + (SUB ? 4 * split + warp : split)) * H + head[rr];
         if ((lane & 3) == 0 && grp == 0) { a.pm[at] = m[rr] * 0.6931471805599453f; a.pl[at] = l[rr]; }     // the maximum back in natural units
         float* dst = a.po + (at * G + c_lo) * Dv;
 #pragma unroll
@@ -287,7 +293,7 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
 // long contexts: `share` = 1) a block takes one (token, head) and deals the pairs to its groups, whose sums meet in shared
 // memory in the order of the groups; with few (prompts) every group takes a head of its own.  A thread's loads do not
 // depend on one another; eight are in flight at a time.
-__global__ void __launch_bounds__(256) flashmix_merge_kernel(FlashMixArgs a, const float* sink, const float* mix, bf16* out, int share) {
+__global__ void __launch_bounds__(1024) flashmix_merge_kernel(FlashMixArgs a, const float* sink, const float* mix, bf16* out, int share) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float merge_s[];
@@ -302,13 +308,18 @@ __global__ void __launch_bounds__(256) flashmix_merge_kernel(FlashMixArgs a, con
         pl_s[e] = a.pl[(size_t)t * S * H + e];
     }
     __syncthreads();
-    for (int g = threadIdx.x; g < H; g += blockDim.x) {
-        float M = sink ? sink[g] : -INFINITY;
-        for (int s = 0; s < S; ++s) M = fmaxf(M, coef[s * H + g]);
-        float den = sink ? expf(sink[g] - M) : 0.f;
-        for (int s = 0; s < S; ++s) if (coef[s * H + g] > -INFINITY) den += pl_s[s * H + g] * expf(coef[s * H + g] - M);
-        M_s[g] = M;
-        inv_s[g] = den > 0.f ? 1.0f / den : 0.f;
+    // a head's maximum and denominator: a warp a head, its lanes dealt the partial results (whole warps only take part)
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    for (int g = wid; wid < n_warps && g < H; g += n_warps) {
+        float M = -INFINITY;
+        for (int s = lane; s < S; s += 32) M = fmaxf(M, coef[s * H + g]);
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        if (sink) M = fmaxf(M, sink[g]);
+        float den = 0.f;
+        for (int s = lane; s < S; s += 32) if (coef[s * H + g] > -INFINITY) den += pl_s[s * H + g] * expf(coef[s * H + g] - M);
+        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+        if (sink) den += expf(sink[g] - M);
+        if (lane == 0) { M_s[g] = M; inv_s[g] = den > 0.f ? 1.0f / den : 0.f; }
     }
     __syncthreads();
     for (int e = threadIdx.x; e < S * H; e += blockDim.x) {
@@ -359,16 +370,21 @@ extern "C" int pe_attention_flashmix_group(int H, int G, int D, int Dv) {
     return cg;
 }
 
-extern "C" long long pe_attention_flashmix_scratch_floats(int T, int splits, int H, int G, int Dv) {
-    return (long long)T * splits * H * (2 + (long long)G * Dv);
+// single != 0: single tokens, whose ranges may be cut in four once more inside a block
+extern "C" long long pe_attention_flashmix_scratch_floats(int T, int splits, int H, int G, int Dv, int single) {
+    return (long long)T * splits * (single ? 4 : 1) * H * (2 + (long long)G * Dv);
 }
 
-template <int DKM, int NVM>
-static int fx_launch(const FlashMixArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
-    PE_TRY(cudaFuncSetAttribute(flashmix_kernel<DKM, NVM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    PE_TRY(pe_launch(flashmix_kernel<DKM, NVM>, grid, FX_THREADS, smem, s, a));
+template <int DKM, int NVM, bool SUB>
+static int fx_launch_as(const FlashMixArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
+    PE_TRY(cudaFuncSetAttribute(flashmix_kernel<DKM, NVM, SUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    PE_TRY(pe_launch(flashmix_kernel<DKM, NVM, SUB>, grid, FX_THREADS, smem, s, a));
     PE_LAUNCH_CHECK();
     return 0;
+}
+template <int DKM, int NVM>
+static int fx_launch(const FlashMixArgs& a, bool sub, dim3 grid, size_t smem, cudaStream_t s) {
+    return sub ? fx_launch_as<DKM, NVM, true>(a, grid, smem, s) : fx_launch_as<DKM, NVM, false>(a, grid, smem, s);
 }
 
 extern "C" int pe_attention_flashmix(const void* q, int q_stride, void* out, const void* k_pool, const void* v_pool,
@@ -383,25 +399,32 @@ extern "C" int pe_attention_flashmix(const void* q, int q_stride, void* out, con
     if (cg == 0 || splits < 1 || splits > 65535 || (tiles && n_runs <= 0)) return PE_ERR_UNSUPPORTED;
     if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15 || (q_stride & 1)) return PE_ERR_UNSUPPORTED;
     const int ngroups = (G + cg - 1) / cg;
+    int merge_threads = Dv >= 256 ? Dv : (256 / Dv) * Dv;                          // whole groups of Dv threads
+    // single tokens whose heads of a key/value head fill one warp's rows: the four warps share a page's keys (where the merge
+    // kernel has room for four times the partial results)
+    const bool sub = !tiles && H / G <= 16 && sizeof(float) * (8 * (size_t)H * splits + 2 * (size_t)H + 1024) <= 48 * 1024;
+    const int parts = sub ? 4 * splits : splits;              // partial results a (token, head)
     float* pm = scratch;
-    float* pl = pm + (size_t)T * splits * H;
-    float* po = pl + (size_t)T * splits * H;
+    float* pl = pm + (size_t)T * parts * H;
+    float* po = pl + (size_t)T * parts * H;
     FlashMixArgs a = {(const bf16*)q, q_stride, (const bf16*)k_pool, (const bf16*)v_pool, table, table_stride, tok_pos, tok_row, tiles,
-                      H, G, D, Dv, window, scale, splits, cg, ngroups, slopes, keep_first, v_ld, pm, pl, po};
-    const size_t smem = 2 * 2 * ((size_t)PE_PAGE * (D + FX_PAD) + (size_t)cg * PE_PAGE * (Dv + FX_PAD));      // two stages of bfloat16
-    const int merge_threads = Dv >= 256 ? Dv : (256 / Dv) * Dv;                    // whole groups of Dv threads
-    const size_t merge_smem = sizeof(float) * (2 * (size_t)H * splits + 2 * (size_t)H + (size_t)merge_threads);
+                      H, G, D, Dv, window, scale, splits, cg, ngroups, slopes, keep_first, v_ld, 0, pm, pl, po};
+    a.v_in_k = (v_pool == k_pool && G == 1 && v_ld == D) ? 1 : 0;                  // one copy of a page serves as keys and values
+    const size_t smem = 2 * 2 * ((size_t)PE_PAGE * (D + FX_PAD) + (a.v_in_k ? 0 : (size_t)cg * PE_PAGE * (Dv + FX_PAD)));      // two stages of bfloat16
+    const size_t merge_smem = sizeof(float) * (2 * (size_t)H * parts + 2 * (size_t)H + 1024);       // (room for the most threads)
     if (smem > 220 * 1024 || merge_smem > 48 * 1024 || H > 65535) return PE_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(tiles ? n_runs : T, (tiles ? H : G) * ngroups, splits);
     const int dk = D / 16, nv = cg * (Dv / 8);
     int rc;
-    if (dk <= 4) rc = nv <= 16 ? fx_launch<4, 16>(a, grid, smem, s) : fx_launch<4, 32>(a, grid, smem, s);
-    else if (dk <= 8) rc = nv <= 16 ? fx_launch<8, 16>(a, grid, smem, s) : fx_launch<8, 32>(a, grid, smem, s);
-    else rc = nv <= 16 ? fx_launch<16, 16>(a, grid, smem, s) : fx_launch<16, 32>(a, grid, smem, s);
+    if (dk <= 4) rc = nv <= 16 ? fx_launch<4, 16>(a, sub, grid, smem, s) : fx_launch<4, 32>(a, sub, grid, smem, s);
+    else if (dk <= 8) rc = nv <= 16 ? fx_launch<8, 16>(a, sub, grid, smem, s) : fx_launch<8, 32>(a, sub, grid, smem, s);
+    else rc = nv <= 16 ? fx_launch<16, 16>(a, sub, grid, smem, s) : fx_launch<16, 32>(a, sub, grid, smem, s);
     if (rc) return rc;
+    a.splits = parts;                                         // what the merge kernel adds up
+    if (parts * (mix ? H : 1) >= 64) merge_threads = (1024 / Dv) * Dv;               // many pairs to add: more groups share them
     const int groups = merge_threads / Dv;
-    const int share = (splits * (mix ? H : 1) >= 64 && groups > 1) ? 1 : 0;          // many pairs to add: the groups share a head
+    const int share = (parts * (mix ? H : 1) >= 64 && groups > 1) ? 1 : 0;           // many pairs to add: the groups share a head
     PE_TRY(pe_launch(flashmix_merge_kernel, dim3(T, share ? H : (H + groups - 1) / groups), merge_threads, merge_smem, s, a, sink, mix,
                      (bf16*)out, share));
     PE_LAUNCH_CHECK();

@@ -288,9 +288,11 @@ def linear_mma(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = 
 def attention_decode(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: int, head_dim: int,
                      k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, table_stride: int,
                      tok_pos: torch.Tensor, tok_row: torch.Tensor, window: Optional[int], scale: float,
-                     max_context: int, out: Optional[torch.Tensor] = None, early_pages: bool = True) -> torch.Tensor:
+                     max_context: int, out: Optional[torch.Tensor] = None, early_pages: bool = True, keep_first: int = 0,
+                     slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of T single tokens (bfloat16) over the cache; ``max_context`` bounds every
-    token's position + 1 and fixes the launch shape.  With ``early_pages`` the kernel copies cache pages
+    token's position + 1 and fixes the launch shape.  ``keep_first``: with a window, a sequence's first so many keys stay
+    visible.  ``slopes`` float32 [H]: slope_h * (i - j) is taken off the score of query i and key j.  With ``early_pages`` the kernel copies cache pages
     while the two kernels before it on the stream may still run: they must have written keys and values
     at each token's own position only (the library's own parts do).  A part that rewrites other cache
     rows shortly before attending passes False: the kernel then starts when everything before it has ended."""
@@ -308,7 +310,8 @@ def attention_decode(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: i
     check(lib.pe_attention_decode(q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
                                   block_table.data_ptr(), table_stride, tok_pos.data_ptr(), tok_row.data_ptr(), T,
                                   n_heads, n_kv_heads, head_dim, window or 0, float(scale), int(max_context),
-                                  1 if early_pages else 0, status_ptr(q.device), stream_ptr()), "attention_decode")
+                                  1 if early_pages else 0, status_ptr(q.device), stream_ptr(), int(keep_first) if window else 0,
+                                  _ptr(slopes)), "attention_decode")
     return out
 
 
@@ -869,6 +872,13 @@ def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, h
             tiles = ctx.scratch["prefill_tiles_128"] = prefill_tiles(ctx.lens, ctx.starts, q.device, PREFILL_TILE_TCGEN05)
         return attention_prefill_tcgen05(q, q_stride, n_heads, n_kv, head_dim, k_pool, v_pool, block_table, table_stride, tiles, T,
                                          window, scale, keep_first=keep_first, slopes=slopes)
+    if (q.dtype == torch.bfloat16 and ctx.one_token_each and sink is None and mix is None and not values_in_keys
+            and head_dim == v_head_dim and attention_prefill_tcgen05_takes(head_dim, scale) and q_stride % 8 == 0
+            and HEADMIX_TENSOR_CORES == "1"):
+        # single tokens at the same sizes: the decode kernel of the plain attention, which knows both as well (the kernels before
+        # it in the stream write no cache row but each token's own)
+        return attention_decode(q, q_stride, n_heads, n_kv, head_dim, k_pool, v_pool, block_table, table_stride, tok_pos, tok_row,
+                                window, scale, ctx.max_context, keep_first=keep_first, slopes=slopes)
     lib = mixers()
     tiles, n_runs = None, 0
     if not ctx.one_token_each:
@@ -890,7 +900,7 @@ def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, h
             # mean more partial outputs to write and merge.  A prompt has blocks enough and is not cut (2,048 tokens: 183 us
             # uncut, 209 us in two ranges).
             splits = max(1, min((224 + blocks - 1) // blocks, (ctx.max_context + 63) // 64, 64))
-            ws = scratch("attention_headmix", 4 * lib.pe_attention_flashmix_scratch_floats(T, splits, n_heads, n_kv, v_head_dim), q.device)
+            ws = scratch("attention_headmix", 4 * lib.pe_attention_flashmix_scratch_floats(T, splits, n_heads, n_kv, v_head_dim, 1 if tiles is None else 0), q.device)
             check(lib.pe_attention_flashmix(q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
                                             block_table.data_ptr(), table_stride, tok_pos.data_ptr(), tok_row.data_ptr(), _ptr(tiles),
                                             n_runs, T, n_heads, n_kv, head_dim, v_head_dim, window or 0, float(scale), _ptr(sink),

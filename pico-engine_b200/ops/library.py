@@ -98,7 +98,7 @@ _EXTRA_SIGNATURES = {
 }
 
 _HEAD_DIM_SIGNATURES = {
-    "pe_attention_decode": [P, I, P, P, P, P, I, P, P, I, I, I, I, I, F, I, I, P, P],
+    "pe_attention_decode": [P, I, P, P, P, P, I, P, P, I, I, I, I, I, F, I, I, P, P, I, P],
     "pe_attention_decode_splits": [I, I, I, I, P],
     "pe_attention_prefill": [P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, F, P],
     "pe_attention_prefill_tcgen05": [P, I, P, P, P, LL, P, I, P, I, I, I, I, I, I, F, I, P, P, P],
@@ -158,7 +158,7 @@ def mixers() -> ctypes.CDLL:
         lib.pe_attention_headmix_scratch_floats.restype = c_longlong
         lib.pe_attention_flashmix_group.argtypes = [I, I, I, I]
         lib.pe_attention_flashmix_group.restype = c_int
-        lib.pe_attention_flashmix_scratch_floats.argtypes = [I, I, I, I, I]
+        lib.pe_attention_flashmix_scratch_floats.argtypes = [I, I, I, I, I, I]
         lib.pe_attention_flashmix_scratch_floats.restype = c_longlong
         lib.pe_attention_headmix_mma_plan.argtypes = [I, I, I, I, ctypes.POINTER(c_int)]
         lib.pe_attention_headmix_mma_plan.restype = c_int

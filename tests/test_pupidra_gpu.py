@@ -258,8 +258,8 @@ def test_window_and_kept_edges_in_prompt_and_decoding(dtype, H, G, D, Dv, window
 @pytest.mark.parametrize("H,G,D,window,keep", [(4, 2, 64, 100, 70), (2, 1, 128, 65, 3), (2, 2, 64, 64, 0), (3, 1, 64, None, 0),
                                                (2, 2, 128, 200, 128), (2, 1, 64, 300, 1)])
 def test_long_prompts_in_bfloat16_at_head_sizes_of_the_tensor_memory_kernel(H, G, D, window, keep):
-    """Prompts long enough that the pages of the kept first keys and the pages of the window lie apart, whole and in portions
-    that begin and end off the borders of pages and of the kernel's runs of tokens."""
+    """Prompts long enough that the pages of the kept first keys and the pages of the window lie apart, whole, in portions
+    that begin and end off the borders of pages and of the kernel's runs of tokens, and with the last 330 tokens one by one."""
     dt, n = torch.bfloat16, 900
     g = torch.Generator().manual_seed(H * 100 + D + (window or 0))
     q, k, v = ((torch.randn(n, h, D, generator=g)).to(dt).float() for h in (H, G, G))
@@ -267,7 +267,7 @@ def test_long_prompts_in_bfloat16_at_head_sizes_of_the_tensor_memory_kernel(H, G
     want = plain.biased_attention(q.double(), k.double(), v.double(), scale, window, keep)
     kp, table = paged(k, dt)
     vp, _ = paged(v, dt)
-    for spans in ([(0, n)], [(0, 130), (130, 133), (133, 517), (517, n)]):
+    for spans in ([(0, n)], [(0, 130), (130, 133), (133, 517), (517, n)], [(0, 570)] + [(p, p + 1) for p in range(570, n)]):
         got = run_attention(q, kp, vp, table, dt, spans, window, keep, scale, plain.distance_slopes(H), D)
         assert (got.double() - want).abs().max() < 2e-2 * max(1.0, float(want.abs().max())), spans[:2]
 
