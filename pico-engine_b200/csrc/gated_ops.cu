@@ -537,11 +537,42 @@ __global__ void weighted_act_kernel(const T* h, T* out, int I, int act, const fl
     }
 }
 
+// bfloat16 with I and group multiples of 8: a thread takes 8 columns of one group with 16-byte accesses, and does not read
+// hidden units whose weight is zero.
+__global__ void weighted_act_vec_kernel(const bf16* h, bf16* out, int I8, int act, const float* colw, int group8, int n_groups, size_t total8) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I8;
+        const int c8 = (int)(idx - t * I8);
+        const float w = colw[t * n_groups + min(c8 / group8, n_groups - 1)];
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (w != 0.f) {
+            v = *reinterpret_cast<const uint4*>(h + idx * 8);
+            __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __bfloat1622float2(p[k]);
+                p[k] = __floats2bfloat162_rn(go_act(f.x, act) * w, go_act(f.y, act) * w);
+            }
+        }
+        *reinterpret_cast<uint4*>(out + idx * 8) = v;
+    }
+}
+
 extern "C" int pe_weighted_act(const void* h, void* out, int dtype, int T, int I, int act, const float* colw, int group, int n_groups,
                                void* stream) {
     if (T <= 0 || I <= 0) return 0;
     if (!colw || group <= 0 || n_groups <= 0) return PE_ERR_UNSUPPORTED;
     const size_t total = (size_t)T * I;
+    if (dtype == PE_BF16 && I % 8 == 0 && group % 8 == 0 && (((uintptr_t)h | (uintptr_t)out) & 15) == 0) {
+        const size_t total8 = total / 8;
+        const int vblocks = (int)((total8 + 255) / 256 < 148 * 16 ? (total8 + 255) / 256 : 148 * 16);
+        PE_TRY(pe_launch(weighted_act_vec_kernel, vblocks, 256, 0, (cudaStream_t)stream, (const bf16*)h, (bf16*)out, I / 8, act, colw, group / 8,
+                         n_groups, total8));
+        PE_LAUNCH_CHECK();
+        return 0;
+    }
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == PE_F32) PE_TRY(pe_launch(weighted_act_kernel<float>, blocks, 256, 0, s, (const float*)h, (float*)out, I, act, colw, group, n_groups, total));

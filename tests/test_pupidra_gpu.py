@@ -421,15 +421,20 @@ def test_routing_over_all_experts(E, top, shared):
     got = kernels.moe_route(z.float().cuda().contiguous(), E, top, extra, over_all=True, factor=1.7)
     assert (got.cpu().double() - want).abs().max() < 1e-5
     # hidden units: relu^2 times the weight of the expert that owns the column; the shared expert's columns come last and may be wider
-    ff, sff = 12, 20
-    h = torch.randn(T, E * ff + (sff if shared else 0), generator=g)
-    for dt, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
-        hh = h.to(dt)
-        out = kernels.weighted_act(hh.cuda().contiguous(), "relu2", got, ff).float().cpu()
-        col = torch.clamp(torch.arange(h.shape[1]) // ff, max=want.shape[1] - 1)
-        ref = plain.relu2(hh.double()) * want[:, col]
-        assert (out.double() - ref).abs().max() < tol * float(ref.abs().max())
-        assert bool((out[ref == 0] == 0).all())
+    # (widths that are multiples of 8 take 16-byte accesses in bfloat16); an infinite hidden unit behind a zero weight gives zero
+    for ff, sff in ((12, 20), (16, 40)):
+        h = torch.randn(T, E * ff + (sff if shared else 0), generator=g)
+        unused = [e for e in range(E) if want[0, e] == 0]
+        if unused:
+            h[0, unused[0] * ff + 1] = float("inf")
+        for dt, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+            hh = h.to(dt)
+            out = kernels.weighted_act(hh.cuda().contiguous(), "relu2", got, ff).float().cpu()
+            col = torch.clamp(torch.arange(h.shape[1]) // ff, max=want.shape[1] - 1)
+            w = want[:, col]
+            ref = torch.where(w == 0, torch.zeros_like(w), plain.relu2(hh.double()) * w)
+            assert (out.double() - ref).abs().max() < tol * float(ref.abs().max())
+            assert bool((out[ref == 0] == 0).all())
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
