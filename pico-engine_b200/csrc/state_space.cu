@@ -133,7 +133,7 @@ __device__ __forceinline__ void ss_find_chunk(const int* row_first, const int* r
 // 2: a chunk from its incoming state, writing outputs.  The recurrence is linear in S (S_end = (prod a) S_in + L), so the three-pass
 // way (1, the carry kernel, 2) equals the walk up to float32 rounding.
 template <typename T, int NRMAX, int MODE>
-__global__ void __launch_bounds__(256) scan_kernel(ScanArgs a) {
+__global__ void __launch_bounds__(256, MODE == 0 ? 1 : 3) scan_kernel(ScanArgs a) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) float ss_smem[];
@@ -167,9 +167,59 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanArgs a) {
     const float A = expf(load_as_f(a.a_log, a.al_dtype, h)), Dh = load_as_f(a.d_skip, a.d_dtype, h), dtb = load_as_f(a.dt_bias, a.dtb_dtype, h);
     float decay = 1.f;                                         // MODE 1: the product of the chunk's decays
     const T* proj = (const T*)a.proj;
+    // Where a group's B, C, x and raw step sizes are few enough a thread (at most SS_PRE entries of B and of C, one of x), they are
+    // fetched into registers while the group before is walked, and go to shared memory after it: the loads' latency lies under the
+    // walk.  Entry k of a thread is element e = tid + k blockDim.x of the group every time, so what it stands for is worked out once:
+    // code = token << 24 | state row n; -2 a padding place (zero), -1 nothing.
+    constexpr int SS_PRE = 6;
+    const bool pre = MODE != 0 && SS_TOKENS * ROW <= SS_PRE * (int)blockDim.x && SS_TOKENS * PT <= (int)blockDim.x;   // (the walk of whole rows, which decoding uses, stages as it goes)
+    int code[SS_PRE];
+    float pb[SS_PRE], pc[SS_PRE], px = 0.f, pdt = 0.f;
+    const float* b_col = a.xbc + inner + g * N;                // B of this head's group; C lies G N columns further
+    const int c_off = a.G * N;
+    const int x_tok = tid / PT, x_col = tid % PT;              // the x entry of this thread
+#pragma unroll
+    for (int k = 0; k < SS_PRE; ++k) {
+        code[k] = -1;
+        pb[k] = pc[k] = 0.f;
+        const int e = tid + k * (int)blockDim.x;
+        if (pre && e < SS_TOKENS * ROW) {
+            const int i = e / ROW, w = e % ROW, sidx = w / NRP, r = w % NRP, n = sidx * NR + r;
+            code[k] = (r < NR && n < N) ? ((i << 24) | n) : -2;
+        }
+    }
+    auto fetch = [&](int c0) {
+        const int nc = min(SS_TOKENS, n_tok - c0);
+#pragma unroll
+        for (int k = 0; k < SS_PRE; ++k) {
+            const int i = code[k] >> 24, n = code[k] & 0xffffff;
+            const bool there = code[k] >= 0 && i < nc;
+            const float* at = b_col + (size_t)(first + c0 + (there ? i : 0)) * a.xbc_ld + (there ? n : 0);
+            pb[k] = there ? at[0] : 0.f;
+            if (MODE != 1) pc[k] = there ? at[c_off] : 0.f;
+        }
+        px = (x_tok < nc && p0 + x_col < P) ? a.xbc[(size_t)(first + c0 + x_tok) * a.xbc_ld + h * P + p0 + x_col] : 0.f;
+        pdt = tid < nc ? to_f(proj[(size_t)(first + c0 + tid) * a.proj_ld + a.dt_off + h]) : 0.f;
+    };
+    if (pre) fetch(0);
     for (int c0 = 0; c0 < n_tok; c0 += SS_TOKENS) {
         const int nc = min(SS_TOKENS, n_tok - c0);
         __syncthreads();                                       // the group before has been walked
+        if (pre) {
+#pragma unroll
+            for (int k = 0; k < SS_PRE; ++k) {
+                if (code[k] != -1) {
+                    Bs[tid + k * (int)blockDim.x] = pb[k];
+                    if (MODE != 1) Cs[tid + k * (int)blockDim.x] = pc[k];
+                }
+            }
+            if (tid < SS_TOKENS * PT) xs[tid] = px;
+            if (tid < nc) {
+                const float dt = ss_softplus(pdt + dtb);
+                dts[tid] = dt;
+                das[tid] = expf(-A * dt);
+            }
+        } else {
         for (int e = tid; e < nc * ROW; e += blockDim.x) {
             const int i = e / ROW, w = e % ROW, s = w / NRP, r = w % NRP, n = s * NR + r;
             const bool there = r < NR && n < N;
@@ -186,6 +236,8 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanArgs a) {
             dts[tid] = dt;
             das[tid] = expf(-A * dt);
         }
+        }
+        if (pre && c0 + SS_TOKENS < n_tok) fetch(c0 + SS_TOKENS);          // the next group's numbers travel during this walk
         __syncthreads();
         for (int i = 0; i < nc; ++i) {
             const float x = xs[i * PT + (on ? pl : 0)];
