@@ -70,6 +70,21 @@ class RotaryPairsSpec(PartSpec):
 
 
 @dataclass(frozen=True)
+class RotaryHalvesSpec(PartSpec):
+    """Rotary encoding of the first ``dims`` entries of a head in the layout of halves: entry i < dims/2 pairs with entry i + dims/2,
+    the pair (u, v) at position p becomes (u cos a - v sin a, v cos a + u sin a), a = p * f_i, f_i = base^(-2i/dims); the other
+    entries of the head stay as they are.  ``stretch`` = (factor, original, fast, slow) lengthens the slow turns: with
+    where(t) = dims * ln(original / (2 pi t)) / (2 ln base), lo = max(floor(where(fast)), 0), hi = min(ceil(where(slow)), dims - 1)
+    and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency is f_i / factor * ramp_i + f_i * (1 - ramp_i), and cos
+    and sin are multiplied by ``magnitude_slope`` * ln(factor) + 1."""
+    head_dim: int
+    dims: int
+    base: float
+    stretch: Optional[Tuple[float, float, float, float]] = None
+    magnitude_slope: float = 0.1
+
+
+@dataclass(frozen=True)
 class SinusoidAddSpec(PartSpec):
     """A position vector added to the embedding: entry 2i of position p is sin(p * base^(-2i/size)),
     entry 2i+1 the cosine of the same angle.  It has no tensors."""
@@ -171,7 +186,12 @@ class GatedAttentionSpec(PartSpec):
     (key j is seen from i iff j <= i and (i - j < window or j < f)).  ``distance_slopes`` (one number a head, or None):
     slope_h * (i - j) is taken off the score of query i and key j before the softmax.  ``bias``: the four projections
     have bias vectors (``name + bias_suffix``).  ``own_kv`` False: the mixer has no key and value projections and reads
-    the keys and values another schedule entry wrote (``ScheduleEntry.cache_of``).  Tensor names are ``prefix + name``."""
+    the keys and values another schedule entry wrote (``ScheduleEntry.cache_of``).  ``fixed_sink`` = z: one more place of score z
+    that carries no value joins every softmax denominator (z = 0: p_j = exp(s_j) / (1 + sum exp(s_j))).  ``value_blend``: the mixers
+    of a model that name the same ``value_blend_key`` share values: the "source" (the first of them in the schedule) uses and caches
+    its own values and shows them to the others; a "reader" uses and caches (1 - l) v + l v_source, v_source the source's values of the
+    same token and l its own stored number ``prefix + value_blend``.  ``position`` may also be a :class:`RotaryHalvesSpec`.
+    Tensor names are ``prefix + name``."""
     hidden: int
     n_heads: int
     n_kv_heads: int
@@ -194,6 +214,10 @@ class GatedAttentionSpec(PartSpec):
     bias_suffix: str = ".b"
     own_kv: bool = True
     cache_span: Optional[Tuple[Optional[int], int]] = None   # (window, keep_first) the cache keeps where other entries that read it see further; None: this mixer's own
+    fixed_sink: Optional[float] = None
+    value_blend: Optional[str] = None                        # tensor name (behind the prefix) of a reader's blending number
+    value_blend_role: Optional[str] = None                   # "source", "reader" or None (values are the mixer's own business)
+    value_blend_key: str = "values"
 
 
 @dataclass(frozen=True)
@@ -202,8 +226,9 @@ class LatentAttentionSpec(PartSpec):
     by head as [``head_dim`` plain | ``rot_dim`` rotated] entries.  W_dkv h has ``kv_rank`` + ``rot_dim`` entries: the first
     ``kv_rank``, RMS-normed (eps ``norm_eps``, plain weight ``dkv_norm``), are the latent row c; the others are one rotated key
     part that all heads share.  Head h's plain key is W_uk,h c and its value W_uv,h c; score = (q_plain . k_plain + q_rot . k_rot)
-    * ``scale``; every earlier key is visible.  ``position`` (a :class:`RotaryPairsSpec` over ``rot_dim`` entries) turns q_rot and
-    k_rot.  Head h's output is multiplied by sigmoid((W_g h)_h), one number a head (``gate`` None: no gate), then W_o.
+    * ``scale``; every earlier key is visible, or with ``window`` = w key j from query i iff 0 <= i - j < w.  With ``q_rank`` the
+    queries pass a low-rank row of their own: q = W_uq (rmsnorm(W_dq h) * ``dq_norm``) instead of W_q h.  ``position`` (a
+    :class:`RotaryPairsSpec` or :class:`RotaryHalvesSpec` over ``rot_dim`` entries, without stretch) turns q_rot and k_rot.  Head h's output is multiplied by sigmoid((W_g h)_h), one number a head (``gate`` None: no gate), then W_o.
     The cache keeps c and the rotated key part, nothing else.  Tensor names are ``prefix + name``."""
     hidden: int
     n_heads: int
@@ -222,6 +247,11 @@ class LatentAttentionSpec(PartSpec):
     uk_name: str = "uk"
     uv_name: str = "uv"
     o_name: str = "o"
+    window: Optional[int] = None
+    q_rank: Optional[int] = None
+    dq_name: str = "dq"
+    dq_norm: str = "dq.norm"
+    uq_name: str = "uq"
 
 
 @dataclass(frozen=True)
@@ -324,11 +354,14 @@ class DenseMLPSpec(PartSpec):
 
 @dataclass(frozen=True)
 class GatedMLPSpec(PartSpec):
-    """down(act(gate(x)) * up(x)), no biases; ``activation`` "gelu_tanh" or "silu".  Tensor names are ``prefix + name``."""
+    """down(act(gate(x)) * up(x)), no biases; ``activation`` "gelu_tanh" or "silu"; or "clamped_sigmoid": with g = min(gate(x), ``limit``)
+    and u = clamp(up(x), -``limit``, ``limit``) the hidden units are g * sigmoid(``alpha`` * g) * (u + 1).  Tensor names are ``prefix + name``."""
     hidden: int
     intermediate: int
     prefix: str
     activation: str = "silu"
+    limit: Optional[float] = None
+    alpha: float = 1.702
     gate_name: str = "gate"
     up_name: str = "up"
     down_name: str = "down"
@@ -342,7 +375,11 @@ class MixtureSpec(PartSpec):
     runs for every token and is added, multiplied by sigmoid(w_sg . h) (``shared_gate_name`` [1, hidden]; None: added as it is).
     ``gated`` False: an expert is down(act(up(x))) and has no gate matrix (``activation`` then also takes "relu2").
     ``scores`` "softmax_all": the weights are the chosen experts' entries of the softmax over all experts, not renormalised
-    ("softmax_chosen": the softmax over the chosen logits alone); either way they are multiplied by ``route_scale``."""
+    ("softmax_chosen": the softmax over the chosen logits alone); either way they are multiplied by ``route_scale``.
+    ``scores`` "sigmoid": a score is the sigmoid of the logit; the choice reads score + ``correction_name`` (a stored vector [n_experts];
+    None: the score alone), first among ``n_groups`` equal runs of neighbouring experts (a run counts the sum of its ``group_best``
+    largest; only the ``keep_groups`` best runs stay), then the ``top_k`` largest of what stays; the weights are the chosen experts'
+    plain scores, not renormalised, times ``route_scale``."""
     hidden: int
     n_experts: int
     top_k: int
@@ -360,6 +397,10 @@ class MixtureSpec(PartSpec):
     gate_name: str = "gate"
     up_name: str = "up"
     down_name: str = "down"
+    correction_name: Optional[str] = None
+    n_groups: int = 1
+    keep_groups: int = 1
+    group_best: int = 2
 
 
 # ------------------------------------------------------------------ layers and the model
@@ -372,7 +413,9 @@ class LayerSpec:
     x += mixer(norm(x)); x += ffn(norm(x))  (pico-engine src/pico_engine/model.py:167-237); "parallel" is
     x += mixer(norm1(x)) + ffn(norm2(x)), both halves reading the same x; "post_norm" is
     x += scale1 * norm1(mixer(x)); x += scale2 * norm2(ffn(x)): the sublayers read the stream as it is and the norms
-    act on their outputs (``mixer_scale`` / ``feed_forward_scale`` name the scale vectors; None: no scale).
+    act on their outputs (``mixer_scale`` / ``feed_forward_scale`` name the scale vectors; None: no scale); "sandwich" is
+    x += out_norm1(mixer(norm1(x))); x += out_norm2(ffn(norm2(x))) with a norm before and one after each sublayer
+    (``mixer_out_norm`` / ``feed_forward_out_norm``).
     Every part is optional: a block without a feed-forward is a mixer-only block (pico-engine's
     recurrent layers are such, src/pico_engine/model.py:389-406), one without a mixer a feed-forward-only
     block, and a half without a norm takes the residual stream as it is.
@@ -387,6 +430,8 @@ class LayerSpec:
     residual_scale: float = 1.0                      # x += residual_scale * sublayer(norm(x))
     mixer_scale: Optional[str] = None                # "post_norm": tensor [hidden] the normed output of the mixer is multiplied by
     feed_forward_scale: Optional[str] = None         # the same for the feed-forward
+    mixer_out_norm: Optional[PartSpec] = None        # "sandwich": the norm of the mixer's output before it is added
+    feed_forward_out_norm: Optional[PartSpec] = None  # the same for the feed-forward
 
 
 @dataclass(frozen=True)
@@ -427,10 +472,13 @@ class ModelPlan:
     logit_softcap: Optional[float] = None            # logits <- cap * tanh(logits / cap); None: logits as projected
     stream_vectors: Tuple[Tuple[str, int], ...] = ()  # (tensor name, rows): [rows, hidden] tensors whose rows schedule entries add to the stream
     embedding_pairs: Optional[PartSpec] = None       # added to the embedding by (previous token, token) (a BigramTableSpec); None: nothing
+    embedding_scale: float = 1.0                     # the embedded token is multiplied by this (the head reads the table as stored)
 
     def validate(self) -> None:
         if not self.layers:
             raise ConfigError("a model needs at least one layer")
+        if self.embedding_scale != 1.0 and self.embedding_pairs is not None:
+            raise ConfigError("an embedding that reads pairs of tokens takes no scale")
         for e, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < len(self.layers):
                 raise ConfigError(f"schedule[{e}] names layer {entry.layer}, but there are {len(self.layers)} layers")

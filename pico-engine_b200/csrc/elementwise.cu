@@ -13,7 +13,7 @@ extern "C" void pe_set_pdl(int on) { pe_pdl_enabled() = on ? 1 : 0; }
 // ---------------------------------------------------------------- embedding
 template <typename TW>
 __global__ void embed_kernel(const TW* table, const int* ids, float* out,
-                             int H, int V) {
+                             int H, int V, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -21,15 +21,15 @@ __global__ void embed_kernel(const TW* table, const int* ids, float* out,
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);          // the host refuses such ids; never read outside the table
     const TW* row = table + (size_t)id * H;
     float* o = out + (size_t)t * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f(row[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f(row[i]) * scale;      // (a scale of 1 leaves the row as stored)
 }
 
-extern "C" int pe_embed(const void* table, int table_dtype, const int* ids, float* out, int T, int H, int V,
+extern "C" int pe_embed(const void* table, int table_dtype, const int* ids, float* out, int T, int H, int V, float scale,
                         void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    if (table_dtype == PE_F32) PE_TRY(pe_launch(embed_kernel<float>, T, 256, 0, s, (const float*)table, ids, out, H, V));
-    else if (table_dtype == PE_BF16) PE_TRY(pe_launch(embed_kernel<bf16>, T, 256, 0, s, (const bf16*)table, ids, out, H, V));
+    if (table_dtype == PE_F32) PE_TRY(pe_launch(embed_kernel<float>, T, 256, 0, s, (const float*)table, ids, out, H, V, scale));
+    else if (table_dtype == PE_BF16) PE_TRY(pe_launch(embed_kernel<bf16>, T, 256, 0, s, (const bf16*)table, ids, out, H, V, scale));
     else return PE_ERR_UNSUPPORTED;
     PE_LAUNCH_CHECK();
     return 0;

@@ -159,6 +159,104 @@ extern "C" int pe_rotary_norm_store(void* qkv, int dtype, int ld, int T, int H, 
     return 0;
 }
 
+// ---------------------------------------------------------------- rotation of halves, blended values, cache write
+// The same rows, with the other layout of a rotation: entry i < rot_dims / 2 of a query or key head pairs with entry i + rot_dims / 2;
+// the pair (u, v) becomes (u c - v s, v c + u s) with c = magnitude * cos(pos * freq[i]), s = magnitude * sin(pos * freq[i]); entries
+// from rot_dims on stay.  Then (norm != 0) the head is divided by sqrt(mean(head^2) + eps).  Values: with `blend` (rows [T, blend_ld]
+// of G * Dv entries in the step's dtype, the values another layer made of the same tokens) every value becomes
+// (1 - lambda) v + lambda blend[t], lambda one stored number; formed in float32 and rounded once.  Heads and values are rewritten in
+// place; keys and values also go to their cache pages.  A warp a head; a lane keeps its entries of the head in registers (D <= 256).
+template <typename T, int NE>
+__global__ void __launch_bounds__(256) rotary_half_store_kernel(T* qkv, int ld, int H, int G, int D, int Dv, const float* freq, int rot_dims,
+                                                                float magnitude, int norm, float eps, const int* tok_pos, const int* tok_row,
+                                                                T* k_pool, T* v_pool, const int* table, int table_stride, int store,
+                                                                const T* blend, int blend_ld, const void* lambda, int lambda_dtype) {
+    pdl_launch_dependents();
+    __shared__ float s_cos[128], s_sin[128];                               // the token's angles, the same for all its heads
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    pdl_wait();
+    T* row = qkv + (size_t)t * ld;
+    const int pos = tok_pos[t];
+    const int half = rot_dims / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * freq[i], &sn, &cs);
+        s_sin[i] = sn * magnitude; s_cos[i] = cs * magnitude;
+    }
+    long long page = -1;
+    if (store) page = table[(size_t)tok_row[t] * table_stride + pos / PE_PAGE];
+    const float lam = blend ? load_as_f(lambda, lambda_dtype, 0) : 0.f;
+    __syncthreads();
+    for (int u = warp; u < H + 2 * G; u += (int)(blockDim.x >> 5)) {
+        if (u < H + G) {
+            T* v = row + (size_t)u * D;
+            float val[NE];
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < NE; ++e) {
+                const int d = lane + 32 * e;
+                float f = 0.f;
+                if (d < D) {
+                    f = to_f(v[d]);
+                    if (d < rot_dims) {
+                        const bool low = d < half;
+                        const int i = low ? d : d - half;
+                        const float other = to_f(v[low ? d + half : d - half]);
+                        f = low ? fmaf(f, s_cos[i], -other * s_sin[i]) : fmaf(f, s_cos[i], other * s_sin[i]);
+                    }
+                }
+                val[e] = f;
+                ss = fmaf(f, f, ss);
+            }
+            const float rstd = norm ? 1.0f / sqrtf(warp_sum(ss) / (float)D + eps) : 1.0f;
+            __syncwarp();                                                  // every lane has read its partners
+            T* dst = (u >= H && store && page >= 0) ? k_pool + (((size_t)page * G + (u - H)) * PE_PAGE + pos % PE_PAGE) * D : nullptr;
+#pragma unroll
+            for (int e = 0; e < NE; ++e) {
+                const int d = lane + 32 * e;
+                if (d < D) {
+                    const T o = from_f<T>(val[e] * rstd);
+                    v[d] = o;
+                    if (dst) dst[d] = o;
+                }
+            }
+        } else {
+            const int c = u - H - G;
+            T* v = row + (size_t)(H + G) * D + (size_t)c * Dv;
+            T* dst = (store && page >= 0) ? v_pool + (((size_t)page * G + c) * PE_PAGE + pos % PE_PAGE) * Dv : nullptr;
+            const T* other = blend ? blend + (size_t)t * blend_ld + (size_t)c * Dv : nullptr;
+            if (!other && !dst) continue;
+            for (int d = lane; d < Dv; d += 32) {
+                T o = v[d];
+                if (other) { o = from_f<T>(fmaf(lam, to_f(other[d]), (1.0f - lam) * to_f(o))); v[d] = o; }
+                if (dst) dst[d] = o;
+            }
+        }
+    }
+}
+
+extern "C" int pe_rotary_half_store(void* qkv, int dtype, int ld, int T, int H, int G, int D, int Dv, const float* freq, int rot_dims,
+                                    float magnitude, int norm, float eps, const int* tok_pos, const int* tok_row, void* k_pool, void* v_pool,
+                                    const int* table, int table_stride, int store, const void* blend, int blend_ld, const void* lambda,
+                                    int lambda_dtype, void* stream) {
+    if (T <= 0) return 0;
+    if (D > 256 || rot_dims > D || (rot_dims & 1) || (rot_dims > 0 && !freq) || ld < (H + G) * D + G * Dv || (blend && (!lambda || blend_ld < G * Dv)))
+        return PE_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = H + 2 * G > 16 ? 256 : 128;
+#define ROTH_LAUNCH(TT, NE) PE_TRY(pe_launch(rotary_half_store_kernel<TT, NE>, T, threads, 0, s, (TT*)qkv, ld, H, G, D, Dv, freq, rot_dims, magnitude, \
+                                             norm, eps, tok_pos, tok_row, (TT*)k_pool, (TT*)v_pool, table, table_stride, store, (const TT*)blend,      \
+                                             blend_ld, lambda, lambda_dtype))
+    if (dtype == PE_F32) {
+        if (D <= 64) ROTH_LAUNCH(float, 2); else if (D <= 128) ROTH_LAUNCH(float, 4); else ROTH_LAUNCH(float, 8);
+    } else if (dtype == PE_BF16) {
+        if (D <= 64) ROTH_LAUNCH(bf16, 2); else if (D <= 128) ROTH_LAUNCH(bf16, 4); else ROTH_LAUNCH(bf16, 8);
+    } else return PE_ERR_UNSUPPORTED;
+#undef ROTH_LAUNCH
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
 // ---------------------------------------------------------------- norm over groups of channels, times a gate
 // in [T, C] (float32 or the step's dtype); group > 0: every run of `group` channels is divided by
 // sqrt(mean(run^2) + eps) and multiplied by weight[channel % group]; then (gate != null) by act(gate[t, g_off + c]) of
@@ -446,13 +544,19 @@ extern "C" int pe_add_rows(float* x, const float* rows, const void* vec, int v_d
 // ---------------------------------------------------------------- gated activation, a weight per group of columns
 // gu [T, 2I] = gate | up; out[t, c] = act(gate[t, c]) * up[t, c] * colw[t, g(c)], with g(c) = min(c / group, n_groups - 1)
 // (colw [T, n_groups] float32 or null: no weights).  The product is formed in float32.
+// act 5, the clamped form: g = min(gate, limit), u = clamp(up, -limit, limit), out = g sigmoid(alpha g) (u + 1).
 template <typename T>
-__global__ void gated_act_kernel(const T* gu, T* out, int I, int act, const float* colw, int group, int n_groups, size_t total) {
+__global__ void gated_act_kernel(const T* gu, T* out, int I, int act, const float* colw, int group, int n_groups, size_t total,
+                                 float limit, float alpha) {
     pdl_launch_dependents();
     pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I, c = idx % I;
-        float f = go_act(to_f(gu[t * 2 * I + c]), act) * to_f(gu[t * 2 * I + I + c]);
+        float f;
+        if (act == 5) {
+            const float g = fminf(to_f(gu[t * 2 * I + c]), limit), u = fminf(fmaxf(to_f(gu[t * 2 * I + I + c]), -limit), limit);
+            f = g * go_sigmoid(alpha * g) * (u + 1.0f);
+        } else f = go_act(to_f(gu[t * 2 * I + c]), act) * to_f(gu[t * 2 * I + I + c]);
         if (colw) {
             const int g = min((int)(c / group), n_groups - 1);
             const float w = colw[t * n_groups + g];
@@ -476,7 +580,8 @@ __device__ __forceinline__ float go_act_fast(float v, int act) {
     if (act == 1) return go_sigmoid_fast(v);
     return v;
 }
-__global__ void gated_act_bf16x8_kernel(const bf16* gu, bf16* out, int I, int act, const float* colw, int group, int n_groups, size_t units) {
+__global__ void gated_act_bf16x8_kernel(const bf16* gu, bf16* out, int I, int act, const float* colw, int group, int n_groups, size_t units,
+                                        float limit, float alpha) {
     pdl_launch_dependents();
     pdl_wait();
     const int per_row = I / 8;
@@ -490,7 +595,12 @@ __global__ void gated_act_bf16x8_kernel(const bf16* gu, bf16* out, int I, int ac
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const float2 gf = __bfloat1622float2(g2[e]), uf = __bfloat1622float2(u2[e]);
-            float a = go_act_fast(gf.x, act) * uf.x, b = go_act_fast(gf.y, act) * uf.y;
+            float a, b;
+            if (act == 5) {
+                const float ga = fminf(gf.x, limit), gb = fminf(gf.y, limit);
+                a = ga * go_sigmoid_fast(alpha * ga) * (fminf(fmaxf(uf.x, -limit), limit) + 1.0f);
+                b = gb * go_sigmoid_fast(alpha * gb) * (fminf(fmaxf(uf.y, -limit), limit) + 1.0f);
+            } else { a = go_act_fast(gf.x, act) * uf.x; b = go_act_fast(gf.y, act) * uf.y; }
             if (colw) {
                 const float wa = colw[t * n_groups + min((int)((c + 2 * e) / group), n_groups - 1)];
                 const float wb = colw[t * n_groups + min((int)((c + 2 * e + 1) / group), n_groups - 1)];
@@ -504,7 +614,7 @@ __global__ void gated_act_bf16x8_kernel(const bf16* gu, bf16* out, int I, int ac
 }
 
 extern "C" int pe_gated_act(const void* gu, void* out, int dtype, int T, int I, int act, const float* colw, int group, int n_groups,
-                            void* stream) {
+                            float limit, float alpha, void* stream) {
     if (T <= 0 || I <= 0) return 0;
     if (colw && (group <= 0 || n_groups <= 0)) return PE_ERR_UNSUPPORTED;
     const size_t total = (size_t)T * I;
@@ -513,12 +623,12 @@ extern "C" int pe_gated_act(const void* gu, void* out, int dtype, int T, int I, 
     if (dtype == PE_BF16 && I % 8 == 0 && !(((uintptr_t)gu | (uintptr_t)out) & 15)) {
         const size_t units = total / 8;
         const int b8 = (int)((units + 255) / 256 < 148 * 16 ? (units + 255) / 256 : 148 * 16);
-        PE_TRY(pe_launch(gated_act_bf16x8_kernel, b8, 256, 0, s, (const bf16*)gu, (bf16*)out, I, act, colw, group, n_groups, units));
+        PE_TRY(pe_launch(gated_act_bf16x8_kernel, b8, 256, 0, s, (const bf16*)gu, (bf16*)out, I, act, colw, group, n_groups, units, limit, alpha));
         PE_LAUNCH_CHECK();
         return 0;
     }
-    if (dtype == PE_F32) PE_TRY(pe_launch(gated_act_kernel<float>, blocks, 256, 0, s, (const float*)gu, (float*)out, I, act, colw, group, n_groups, total));
-    else if (dtype == PE_BF16) PE_TRY(pe_launch(gated_act_kernel<bf16>, blocks, 256, 0, s, (const bf16*)gu, (bf16*)out, I, act, colw, group, n_groups, total));
+    if (dtype == PE_F32) PE_TRY(pe_launch(gated_act_kernel<float>, blocks, 256, 0, s, (const float*)gu, (float*)out, I, act, colw, group, n_groups, total, limit, alpha));
+    else if (dtype == PE_BF16) PE_TRY(pe_launch(gated_act_kernel<bf16>, blocks, 256, 0, s, (const bf16*)gu, (bf16*)out, I, act, colw, group, n_groups, total, limit, alpha));
     else return PE_ERR_UNSUPPORTED;
     PE_LAUNCH_CHECK();
     return 0;
@@ -727,6 +837,115 @@ extern "C" int pe_moe_route(const float* logits, int ld, int E, int top, int ext
     if (E <= 0 || E > 2048 || top <= 0 || top > E || extra < 0 || extra > 2) return PE_ERR_UNSUPPORTED;
     PE_TRY(pe_launch(moe_route_kernel, (T + 3) / 4, 128, 0, (cudaStream_t)stream, logits, ld, E, top, extra, weights, ids, T, over_all,
                      factor));
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- the choice of experts among groups, sigmoid scores
+// logits [T, ld] float32.  Scores s = sigmoid(logit).  The choice reads c = s + correction (a stored vector [E], or null: zeros):
+// the experts form `n_groups` equal runs of neighbours; a run counts the sum of its `group_best` largest c; the `keep` runs that
+// count most stay, every other run's c is minus infinity; of what stays the `top` largest c are chosen (of equal numbers the
+// lower index first, for runs and for experts).  weights [T, E] float32: factor * s at the chosen places, zero elsewhere;
+// ids [T, top] int32 (or null) receives the chosen experts, largest c first.  A warp a token, four tokens a block.
+#define MG_MAX_E 1024
+#define MG_MAX_GROUPS 64
+__global__ void __launch_bounds__(128) moe_route_grouped_kernel(const float* logits, int ld, int E, int top, const void* corr, int corr_dtype,
+                                                                int n_groups, int keep, int group_best, float factor, float* weights,
+                                                                int* ids, int T) {
+    pdl_launch_dependents();
+    __shared__ float s_c[4][MG_MAX_E];
+    __shared__ float s_g[4][MG_MAX_GROUPS];
+    const int wi = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + wi;
+    pdl_wait();
+    if (t >= T) return;
+    const float* z = logits + (size_t)t * ld;
+    float* c = s_c[wi];
+    float* gs = s_g[wi];
+    float* w = weights + (size_t)t * E;
+    for (int e = lane; e < E; e += 32) {
+        c[e] = go_sigmoid(z[e]) + (corr ? load_as_f(corr, corr_dtype, e) : 0.f);
+        w[e] = 0.f;
+    }
+    __syncwarp();
+    if (n_groups > 1 && keep < n_groups) {
+        const int per = E / n_groups;
+        for (int g = 0; g < n_groups; ++g) {
+            unsigned long long taken = 0ull;
+            float total = 0.f;
+            for (int b = 0; b < group_best && b < per; ++b) {
+                float best = -INFINITY;
+                int at = 0x7fffffff;
+                for (int j = lane, i = 0; j < per; j += 32, ++i) {
+                    if (taken >> i & 1ull) continue;
+                    const float v = c[g * per + j];
+                    if (v > best || (v == best && j < at)) { best = v; at = j; }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                    const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                    if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+                }
+                if (at == 0x7fffffff) break;
+                if ((at & 31) == lane) taken |= 1ull << (at >> 5);
+                total += best;
+            }
+            if (lane == 0) gs[g] = total;
+        }
+        __syncwarp();
+        // a run that stays is marked in place: its count becomes +infinity
+        for (int k = 0; k < keep; ++k) {
+            float best = -INFINITY;
+            int at = 0x7fffffff;
+            for (int g = lane; g < n_groups; g += 32) {
+                const float v = gs[g];
+                if (v == INFINITY) continue;
+                if (v > best || (v == best && g < at) || at == 0x7fffffff) { best = v; at = g; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (oa != 0x7fffffff && (at == 0x7fffffff || ob > best || (ob == best && oa < at))) { best = ob; at = oa; }
+            }
+            if (at == 0x7fffffff) break;
+            if (lane == 0) gs[at] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (gs[e / per] != INFINITY) c[e] = -INFINITY;
+        __syncwarp();
+    }
+    unsigned long long taken = 0ull;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int e = lane, i = 0; e < E; e += 32, ++i) {
+            if (taken >> i & 1ull) continue;
+            const float v = c[e];
+            if (v > best || (v == best && e < at) || at == 0x7fffffff) { best = v; at = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (oa != 0x7fffffff && (at == 0x7fffffff || ob > best || (ob == best && oa < at))) { best = ob; at = oa; }
+        }
+        if (at == 0x7fffffff) break;
+        if ((at & 31) == lane) taken |= 1ull << (at >> 5);
+        if (lane == 0) { w[at] = factor * go_sigmoid(z[at]); if (ids) ids[k] = at; }
+    }
+}
+
+extern "C" int pe_moe_route_grouped(const float* logits, int ld, int E, int top, const void* corr, int corr_dtype, int n_groups, int keep,
+                                    int group_best, float factor, float* weights, int* ids, int T, void* stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || E > MG_MAX_E || top <= 0 || top > E || n_groups <= 0 || n_groups > MG_MAX_GROUPS || E % n_groups || keep <= 0 || keep > n_groups ||
+        group_best <= 0 || ld < E)
+        return PE_ERR_UNSUPPORTED;
+    PE_TRY(pe_launch(moe_route_grouped_kernel, (T + 3) / 4, 128, 0, (cudaStream_t)stream, logits, ld, E, top, corr, corr_dtype, n_groups, keep,
+                     group_best, factor, weights, ids, T));
     PE_LAUNCH_CHECK();
     return 0;
 }

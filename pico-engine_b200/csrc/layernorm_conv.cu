@@ -318,3 +318,56 @@ extern "C" int pe_dual_layernorm_conv(const float* x, const void* w1, int w1_dty
     }
     return 0;
 }
+
+// ---------------------------------------------------------------- a sublayer's output, layer-normed, into the stream
+// x[t] += layernorm(y[t]) * w + b on the float32 stream (y float32 or bfloat16); with `out` also out[t] = layernorm(x[t]) * w2 + b2
+// of the row as it then stands (the norm in front of the sublayer that reads the stream next), stored in out's dtype.  Both norms
+// in float32, two passes each (mean, then squared deviations).  A block a token; a thread rereads only entries it wrote itself.
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(LN_THREADS) layernorm_add_kernel(float* x, const TY* y, const void* w, int w_dtype, const void* b, int b_dtype,
+                                                                   float eps, int H, const void* w2, int w2_dtype, const void* b2, int b2_dtype,
+                                                                   float eps2, TO* out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const TY* yr = y + (size_t)blockIdx.x * H;
+    float* xr = x + (size_t)blockIdx.x * H;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) s += to_f(yr[i]);
+    const float mean = block_sum(s, scratch) / (float)H;
+    float v = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) { const float d = to_f(yr[i]) - mean; v = fmaf(d, d, v); }
+    const float rstd = 1.0f / sqrtf(block_sum(v, scratch) / (float)H + eps);
+    float s2 = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float n = xr[i] + ((to_f(yr[i]) - mean) * rstd * load_as_f(w, w_dtype, i) + load_as_f(b, b_dtype, i));
+        xr[i] = n;
+        s2 += n;
+    }
+    if (!out) return;
+    const float mean2 = block_sum(s2, scratch) / (float)H;
+    float v2 = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) { const float d = xr[i] - mean2; v2 = fmaf(d, d, v2); }
+    const float rstd2 = 1.0f / sqrtf(block_sum(v2, scratch) / (float)H + eps2);
+    TO* o = out + (size_t)blockIdx.x * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        o[i] = from_f<TO>((xr[i] - mean2) * rstd2 * load_as_f(w2, w2_dtype, i) + load_as_f(b2, b2_dtype, i));
+}
+
+extern "C" int pe_layernorm_add(float* x, const void* y, int y_dtype, const void* w, int w_dtype, const void* b, int b_dtype, float eps,
+                                int T, int H, const void* w2, int w2_dtype, const void* b2, int b2_dtype, float eps2, void* out,
+                                int out_dtype, void* stream) {
+    if (T <= 0) return 0;
+    if (out && (!w2 || !b2)) return PE_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+#define LNA(TY, TO) PE_TRY(pe_launch(layernorm_add_kernel<TY, TO>, T, LN_THREADS, 0, s, x, (const TY*)y, w, w_dtype, b, b_dtype, eps, H, w2, \
+                                     w2_dtype, b2, b2_dtype, eps2, (TO*)out))
+    const bool obf = out && out_dtype == PE_BF16;
+    if (out && out_dtype != PE_BF16 && out_dtype != PE_F32) return PE_ERR_UNSUPPORTED;
+    if (y_dtype == PE_F32) { if (obf) LNA(float, bf16); else LNA(float, float); }
+    else if (y_dtype == PE_BF16) { if (obf) LNA(bf16, bf16); else LNA(bf16, float); }
+    else return PE_ERR_UNSUPPORTED;
+#undef LNA
+    PE_LAUNCH_CHECK();
+    return 0;
+}

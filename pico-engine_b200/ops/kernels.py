@@ -39,8 +39,8 @@ def _code(t: torch.Tensor, name: str) -> int:
         raise KernelError(f"{name} must be float32 or bfloat16, not {t.dtype}") from None
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Rows ``ids`` (int32, [T]) of ``table`` [V, H] as float32 [T, H]."""
+def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+    """Rows ``ids`` (int32, [T]) of ``table`` [V, H] as float32 [T, H], multiplied by ``scale``."""
     V, H = table.shape
     T = ids.shape[0]
     _need(table, "table"); _need(ids, "ids", torch.int32, (T,))
@@ -48,7 +48,7 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = 
         out = torch.empty(T, H, dtype=torch.float32, device=table.device)
     _need(out, "out", torch.float32, (T, H))
     check(core().pe_embed(table.data_ptr(), _code(table, "table"), ids.data_ptr(), out.data_ptr(), T, H, V,
-                          stream_ptr()), "embed")
+                          float(scale), stream_ptr()), "embed")
     return out
 
 
@@ -943,7 +943,7 @@ def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, h
 # ---------------------------------------------------------------------------- gated mixers and routed feed-forwards
 
 LA_ACTIVATIONS = {"none": 0, "silu": 1}
-GATE_ACTIVATIONS = {"none": 0, "sigmoid": 1, "silu": 2, "gelu_tanh": 3, "relu2": 4}
+GATE_ACTIVATIONS = {"none": 0, "sigmoid": 1, "silu": 2, "gelu_tanh": 3, "relu2": 4, "clamped_sigmoid": 5}
 
 
 def linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, n_heads: int, head_dim: int, v_head_dim: int,
@@ -1060,9 +1060,11 @@ def add_rows(x: torch.Tensor, rows: Optional[torch.Tensor], vec: Optional[torch.
     return x
 
 
-def gated_act(gate_up: torch.Tensor, activation: str, col_weights: Optional[torch.Tensor] = None, group: int = 0) -> torch.Tensor:
+def gated_act(gate_up: torch.Tensor, activation: str, col_weights: Optional[torch.Tensor] = None, group: int = 0,
+              limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
     """act(gate) * up [T, I] for gate_up [T, 2I] = gate | up.  ``col_weights`` float32 [T, n]: column c is also multiplied by
-    col_weights[t, min(c // group, n - 1)] (a zero weight gives an exact zero)."""
+    col_weights[t, min(c // group, n - 1)] (a zero weight gives an exact zero).  ``activation`` "clamped_sigmoid": with
+    g = min(gate, limit) and u = clamp(up, -limit, limit) the result is g * sigmoid(alpha * g) * (u + 1)."""
     T, I2 = gate_up.shape
     _need(gate_up, "gate_up")
     n = 0
@@ -1071,7 +1073,7 @@ def gated_act(gate_up: torch.Tensor, activation: str, col_weights: Optional[torc
         _need(col_weights, "col_weights", torch.float32, (T, n))
     out = torch.empty(T, I2 // 2, dtype=gate_up.dtype, device=gate_up.device)
     check(gated().pe_gated_act(gate_up.data_ptr(), out.data_ptr(), _code(gate_up, "gate_up"), T, I2 // 2, GATE_ACTIVATIONS[activation],
-                               _ptr(col_weights), group, n, stream_ptr()), "gated_act")
+                               _ptr(col_weights), group, n, float(limit), float(alpha), stream_ptr()), "gated_act")
     return out
 
 
@@ -1233,11 +1235,13 @@ def gate_norm(y: torch.Tensor, group: int, proj: torch.Tensor, gate_offset: int,
 
 def latent_prepare(proj: torch.Tensor, n_heads: int, head_dim: int, rot_dim: int, rank: int, dkv_offset: int, norm_weight: torch.Tensor,
                    eps: float, freq: Optional[torch.Tensor], rot_dims: int, q_absorbed: torch.Tensor, tok_pos: torch.Tensor,
-                   tok_row: torch.Tensor, k_pool: Optional[torch.Tensor], block_table: Optional[torch.Tensor], table_stride: int) -> torch.Tensor:
+                   tok_row: torch.Tensor, k_pool: Optional[torch.Tensor], block_table: Optional[torch.Tensor], table_stride: int,
+                   halves: bool = False, q_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Queries [T, H * (rank + rot_dim)] = [absorbed plain part | turned rotated part] a head, from ``q_absorbed`` [H, T, rank] and the
     rotated parts of the queries in proj [T, ld] (a head = head_dim plain | rot_dim rotated entries); the row [rmsnorm(first rank
     entries at ``dkv_offset``) * norm_weight | turned last rot_dim entries] goes to the token's place in ``k_pool`` [pages, 1, PAGE,
-    rank + rot_dim] (skipped when None)."""
+    rank + rot_dim] (skipped when None).  ``halves``: the rotation pairs entry i with entry i + rot_dims / 2 instead of neighbours.
+    ``q_rows`` [T, H * (head_dim + rot_dim)]: the queries lie there and not at the front of proj's rows."""
     from .library import state_space
     T, ld = proj.shape
     H, W = n_heads, rank + rot_dim
@@ -1249,11 +1253,14 @@ def latent_prepare(proj: torch.Tensor, n_heads: int, head_dim: int, rot_dim: int
         _need(k_pool, "k_pool", proj.dtype); _need(block_table, "block_table", torch.int32)
         if tuple(k_pool.shape[1:]) != (1, PAGE, W):
             raise KernelError(f"the cache pool must be [pages, 1, {PAGE}, {W}], not {tuple(k_pool.shape)}")
+    if q_rows is not None:
+        _need(q_rows, "q_rows", proj.dtype, (T, H * (head_dim + rot_dim)))
     q = torch.empty(T, H * W, dtype=proj.dtype, device=proj.device)
     check(state_space().pe_latent_prepare(proj.data_ptr(), _code(proj, "proj"), ld, T, H, head_dim, rot_dim, rank, dkv_offset,
                                           norm_weight.data_ptr(), _code(norm_weight, "norm_weight"), float(eps), _ptr(freq), rot_dims,
                                           q_absorbed.data_ptr(), q.data_ptr(), tok_pos.data_ptr(), tok_row.data_ptr(), _ptr(k_pool),
-                                          _ptr(block_table), table_stride, 1 if store else 0, stream_ptr()), "latent_prepare")
+                                          _ptr(block_table), table_stride, 1 if store else 0, 1 if halves else 0, _ptr(q_rows),
+                                          0 if q_rows is None else q_rows.shape[1], stream_ptr()), "latent_prepare")
     return q
 
 
@@ -1268,4 +1275,90 @@ def head_gate(o: torch.Tensor, proj: Optional[torch.Tensor], gate_offset: int) -
     out = torch.empty(T, H * Dv, dtype=o.dtype, device=o.device)
     check(state_space().pe_head_gate(o.data_ptr(), _code(o, "o"), _ptr(proj), 0 if proj is None else proj.shape[1], gate_offset, T, H, Dv,
                                      out.data_ptr(), stream_ptr()), "head_gate")
+    return out
+
+
+def rmsnorm_cols(rows: torch.Tensor, offset: int, cols: int, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """[T, cols] in rows' dtype: the RMS norm (float32) of columns ``offset`` .. ``offset + cols`` of rows [T, ld], times ``weight`` [cols]."""
+    from .library import state_space
+    T, ld = rows.shape
+    _need(rows, "rows"); _need(weight, "weight", None, (cols,))
+    out = torch.empty(T, cols, dtype=rows.dtype, device=rows.device)
+    check(state_space().pe_rmsnorm_cols(rows.data_ptr(), _code(rows, "rows"), ld, offset, cols, weight.data_ptr(), _code(weight, "weight"),
+                                        float(eps), out.data_ptr(), T, stream_ptr()), "rmsnorm_cols")
+    return out
+
+
+# ---------------------------------------------------------------------------- rotation of halves with blended values; norms on outputs
+
+def rotary_half_store(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, v_head_dim: int, freq: Optional[torch.Tensor],
+                      rot_dims: int, magnitude: float, unit_norm: bool, eps: float, tok_pos: torch.Tensor, tok_row: torch.Tensor,
+                      k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], block_table: Optional[torch.Tensor],
+                      table_stride: int, blend: Optional[torch.Tensor] = None, blend_weight: Optional[torch.Tensor] = None) -> None:
+    """In every query and key head of qkv [T, ld] (a row begins with H*D query, G*D key and G*Dv value entries), in place: entry
+    i < rot_dims / 2 and entry i + rot_dims / 2 are turned by pos * freq[i] with cos and sin multiplied by ``magnitude``; then
+    (``unit_norm``) the head is divided by its root mean square.  ``blend`` (a view [T, G*Dv] of rows in qkv's dtype whose row stride
+    may be wider; ``blend_weight`` one stored number l): values become (1 - l) v + l blend.  Keys and values then go to their cache
+    pages (skipped when ``k_pool`` is None)."""
+    T, ld = qkv.shape
+    _need(qkv, "qkv")
+    if ld < n_heads * head_dim + n_kv * head_dim + n_kv * v_head_dim:
+        raise KernelError("queries, keys and values do not fit the rows of qkv")
+    if rot_dims:
+        _need(freq, "freq", torch.float32, (rot_dims // 2,))
+    store = k_pool is not None
+    if store:
+        _need(k_pool, "k_pool", qkv.dtype); _need(v_pool, "v_pool", qkv.dtype); _need(block_table, "block_table", torch.int32)
+        if tuple(k_pool.shape[1:]) != (n_kv, PAGE, head_dim) or tuple(v_pool.shape[1:]) != (n_kv, PAGE, v_head_dim):
+            raise KernelError(f"cache pools must be [pages, {n_kv}, {PAGE}, {head_dim}] and [pages, {n_kv}, {PAGE}, {v_head_dim}], "
+                              f"not {tuple(k_pool.shape)} and {tuple(v_pool.shape)}")
+    blend_ld = 0
+    if blend is not None:
+        if (blend.dtype != qkv.dtype or blend.device != qkv.device or tuple(blend.shape) != (T, n_kv * v_head_dim) or blend.stride(1) != 1
+                or blend_weight is None or blend_weight.numel() != 1):
+            raise KernelError("blend must be [T, G * Dv] rows of qkv's dtype with unit column stride, and blend_weight one number")
+        blend_ld = blend.stride(0)
+    check(gated().pe_rotary_half_store(qkv.data_ptr(), _code(qkv, "qkv"), ld, T, n_heads, n_kv, head_dim, v_head_dim, _ptr(freq), rot_dims,
+                                       float(magnitude), 1 if unit_norm else 0, float(eps), tok_pos.data_ptr(), tok_row.data_ptr(),
+                                       _ptr(k_pool), _ptr(v_pool), _ptr(block_table), table_stride, 1 if store else 0, _ptr(blend), blend_ld,
+                                       _ptr(blend_weight), 0 if blend_weight is None else _code(blend_weight, "blend_weight"), stream_ptr()),
+          "rotary_half_store")
+
+
+def layernorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float,
+                  then: Optional[tuple] = None, out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """x += layernorm(y) * weight + bias on the float32 stream [T, W] (y float32 or bfloat16).  ``then`` = (weight2, bias2, eps2):
+    also returns layernorm(x) * weight2 + bias2 of the rows as they then stand, in ``out_dtype``; one kernel either way."""
+    T, W = x.shape
+    _need(x, "x", torch.float32); _need(y, "y", None, (T, W)); _need(weight, "weight", None, (W,)); _need(bias, "bias", None, (W,))
+    out = None
+    w2 = b2 = None
+    eps2 = 0.0
+    if then is not None:
+        w2, b2, eps2 = then
+        _need(w2, "weight2", None, (W,)); _need(b2, "bias2", None, (W,))
+        out = torch.empty(T, W, dtype=out_dtype, device=x.device)
+    check(mixers().pe_layernorm_add(x.data_ptr(), y.data_ptr(), _code(y, "y"), weight.data_ptr(), _code(weight, "weight"), bias.data_ptr(),
+                                    _code(bias, "bias"), float(eps), T, W, _ptr(w2), 0 if w2 is None else _code(w2, "weight2"), _ptr(b2),
+                                    0 if b2 is None else _code(b2, "bias2"), float(eps2), _ptr(out), 0 if out is None else _code(out, "out"),
+                                    stream_ptr()), "layernorm_add")
+    return out
+
+
+def moe_route_grouped(logits: torch.Tensor, n_experts: int, top_k: int, correction: Optional[torch.Tensor], n_groups: int, keep: int,
+                      group_best: int = 2, factor: float = 1.0, ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Dense routing weights float32 [T, E] from router logits float32 [T, E] with sigmoid scores.  The choice reads score +
+    ``correction`` [E]: experts form ``n_groups`` equal runs of neighbours, a run counts the sum of its ``group_best`` largest, the
+    ``keep`` best runs stay, and of their experts the ``top_k`` largest are chosen.  The weights are ``factor`` times the chosen
+    experts' plain scores (not renormalised), zero elsewhere.  ``ids`` int32 [T, top_k] receives the chosen experts."""
+    T = logits.shape[0]
+    _need(logits, "logits", torch.float32, (T, n_experts))
+    if correction is not None:
+        _need(correction, "correction", None, (n_experts,))
+    if ids is not None:
+        _need(ids, "ids", torch.int32, (T, top_k))
+    out = torch.empty(T, n_experts, dtype=torch.float32, device=logits.device)
+    check(gated().pe_moe_route_grouped(logits.data_ptr(), logits.shape[1], n_experts, top_k, _ptr(correction),
+                                       0 if correction is None else _code(correction, "correction"), n_groups, keep, group_best,
+                                       float(factor), out.data_ptr(), _ptr(ids), T, stream_ptr()), "moe_route_grouped")
     return out

@@ -30,7 +30,7 @@ STATE_SOURCES = ("state_space.cu", "latent_ops.cu")
 HEAD_DIM_SOURCES = ("attention_decode.cu", "attention_prefill.cu", "attention_prefill_tcgen05.cu")      # compiled per head size
 
 _SIGNATURES = {
-    "pe_embed": [P, I, P, P, I, I, I, P],
+    "pe_embed": [P, I, P, P, I, I, I, F, P],
     "pe_embed_pairs": [P, P, I, P, P, P, P, P, P, LL, P, I, I, I, I, I, I, P],
     "pe_select_tokens": [P, P, P, I, P],
     "pe_rmsnorm": [P, P, P, I, F, P, I, I, I, P],
@@ -56,6 +56,7 @@ _SIGNATURES = {
 
 _MIXER_SIGNATURES = {
     "pe_layernorm": [P, P, P, I, P, I, F, P, I, I, I, P],
+    "pe_layernorm_add": [P, P, I, P, I, P, I, F, I, I, P, I, P, I, F, P, I, P],
     "pe_causal_conv_add": [P, P, I, P, LL, P, P, P, P, I, I, I, I, P],
     "pe_conv_state_update": [P, P, LL, P, P, P, I, I, I, P],
     "pe_dual_layernorm_conv": [P, P, I, P, I, P, I, P, P, P, I, P, I, P, I, P, P, I, LL, P, P, P, P, F, I, I, I, I, I, P],
@@ -73,9 +74,11 @@ _GATED_SIGNATURES = {
     "pe_normed_sum_add": [P, P, P, P, P, I, P, P, P, P, I, I, I, I, F, F, P],
     "pe_scaled_add": [P, P, I, F, LL, P],
     "pe_add_rows": [P, P, P, I, I, I, P],
-    "pe_gated_act": [P, P, I, I, I, I, P, I, I, P],
+    "pe_gated_act": [P, P, I, I, I, I, P, I, I, F, F, P],
     "pe_weighted_act": [P, P, I, I, I, I, P, I, I, P],
     "pe_moe_route": [P, I, I, I, I, P, P, I, I, F, P],
+    "pe_moe_route_grouped": [P, I, I, I, P, I, I, I, I, F, P, P, I, P],
+    "pe_rotary_half_store": [P, I, I, I, I, I, I, I, P, I, F, I, F, P, P, P, P, P, I, I, P, I, P, I, P],
     "pe_moe_route_stream": [P, P, I, F, P, I, I, I, I, P, P, I, I, F, P],
 }
 
@@ -83,7 +86,8 @@ _STATE_SIGNATURES = {
     "pe_conv_silu": [P, I, I, I, I, I, P, I, P, I, P, LL, P, P, P, P, P, I, I, P],
     "pe_state_space_scan": [P, I, P, I, I, I, P, I, P, I, P, I, P, LL, P, P, P, P, I, I, I, I, I, I, I, P, P],
     "pe_gate_norm": [P, I, I, I, P, I, I, I, P, I, F, P, P],
-    "pe_latent_prepare": [P, I, I, I, I, I, I, I, I, P, I, F, P, I, P, P, P, P, P, P, I, I, P],
+    "pe_latent_prepare": [P, I, I, I, I, I, I, I, I, P, I, F, P, I, P, P, P, P, P, P, I, I, I, P, I, P],
+    "pe_rmsnorm_cols": [P, I, I, I, I, P, I, F, P, I, P],
     "pe_head_gate": [P, I, P, I, I, I, I, I, P, P],
 }
 

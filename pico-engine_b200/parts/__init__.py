@@ -16,7 +16,7 @@ from .branch_sum import BranchSum
 from .mixture import Mixture
 from .attention_latent import LatentAttention
 from .state_space import StateSpace
-from .block import Layer, parallel, post_norm, pre_norm
+from .block import Layer, parallel, post_norm, pre_norm, sandwich
 from .model import DecoderModel
 
 __all__ = ["ARRANGEMENTS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "FeedForward", "KVView", "Mixer", "Norm",
@@ -24,4 +24,4 @@ __all__ = ["ARRANGEMENTS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "Fee
            "register_mixer", "register_norm", "register_position", "RMSNorm", "NoPosition", "RotaryHalf",
            "GQAAttention", "SwiGLU", "Layer", "pre_norm", "DecoderModel", "LayerNorm", "SinusoidAdd", "CausalConvAdd",
            "HeadMixAttention", "MinGRU", "DenseMLP", "parallel", "GatedMLP", "LinearAttention", "GatedAttention", "BranchSum", "Mixture",
-           "LatentAttention", "StateSpace", "post_norm"]
+           "LatentAttention", "StateSpace", "post_norm", "sandwich"]

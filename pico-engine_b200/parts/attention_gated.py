@@ -4,7 +4,9 @@ from __future__ import annotations
 import torch
 
 from ..cache import CacheNeeds, KVNeed
-from ..config.specs import ConfigError, GatedAttentionSpec, NoPositionSpec, RotaryPairsSpec
+import math
+
+from ..config.specs import ConfigError, GatedAttentionSpec, NoPositionSpec, RotaryHalvesSpec, RotaryPairsSpec
 from ..ops import kernels, linear
 from ..weights.loader import ParamSpec
 from .base import Mixer, first_product, last_product_into, normed_rows, register_mixer
@@ -14,6 +16,26 @@ def pair_frequencies(spec: RotaryPairsSpec, device) -> torch.Tensor:
     """base^(-2i/dims) / factor for i < dims / 2, worked out in float64 and rounded once to float32."""
     i = torch.arange(spec.dims // 2, dtype=torch.float64)
     return (spec.base ** (-2.0 * i / spec.dims) / spec.factor).to(torch.float32).to(device)
+
+
+def halves_frequencies(spec: RotaryHalvesSpec, device):
+    """(frequencies float32 [dims / 2], the factor on cos and sin) of a rotation in the layout of halves: base^(-2i/dims), each
+    stretched by ``spec.stretch`` where that is given; worked out in float64 and rounded once to float32."""
+    half = spec.dims // 2
+    f = [spec.base ** (-2.0 * i / spec.dims) for i in range(half)]
+    magnitude = 1.0
+    if spec.stretch is not None and half:
+        factor, original, fast, slow = spec.stretch
+
+        def where(turns: float) -> float:
+            return spec.dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(spec.base))
+        lo = max(math.floor(where(fast)), 0)
+        hi = min(math.ceil(where(slow)), spec.dims - 1)
+        for i in range(half):
+            ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            f[i] = f[i] / factor * ramp + f[i] * (1.0 - ramp)
+        magnitude = spec.magnitude_slope * math.log(factor) + 1.0
+    return torch.tensor(f, dtype=torch.float64).to(torch.float32).to(device), magnitude
 
 
 @register_mixer(GatedAttentionSpec)
@@ -29,8 +51,14 @@ class GatedAttention(Mixer):
         super().__init__(spec, dtype, device)
         if spec.n_heads % spec.n_kv_heads:
             raise ConfigError(f"{spec.n_heads} query heads cannot share {spec.n_kv_heads} key/value heads evenly")
-        if not isinstance(spec.position, (NoPositionSpec, RotaryPairsSpec)):
-            raise ConfigError("gated attention takes rotation of pairs or no position encoding")
+        if not isinstance(spec.position, (NoPositionSpec, RotaryPairsSpec, RotaryHalvesSpec)):
+            raise ConfigError("gated attention takes rotation of pairs, of halves, or no position encoding")
+        if isinstance(spec.position, RotaryHalvesSpec) and (spec.position.dims % 2 or spec.position.dims > spec.head_dim):
+            raise ConfigError(f"{spec.position.dims} rotated entries do not fit a head of {spec.head_dim}")
+        if spec.value_blend_role not in (None, "source", "reader") or (spec.value_blend_role == "reader") != (spec.value_blend is not None):
+            raise ConfigError("value_blend_role is \"source\", \"reader\" (with the name of its number) or None")
+        if spec.value_blend_role is not None and not (spec.own_kv and isinstance(spec.position, RotaryHalvesSpec)):
+            raise ConfigError("values are blended in the kernel that rotates halves, for a mixer with keys and values of its own")
         if spec.head_dim > 256 or spec.v_head_dim > 256:
             raise ConfigError(f"head sizes {spec.head_dim}/{spec.v_head_dim} are not taken: up to 256 are")
         if spec.window is not None and spec.window <= 0:
@@ -40,11 +68,12 @@ class GatedAttention(Mixer):
             raise ConfigError(f"{len(spec.distance_slopes)} distance slopes for {spec.n_heads} heads")
         if spec.keep_first < 0 or (spec.keep_first and spec.window is None):
             raise ConfigError("keep_first belongs to a window and cannot be negative")
-        self.w_in = self.w_o = self.freq = self.b_in = self.b_o = self.slopes = None
+        self.w_in = self.w_o = self.freq = self.b_in = self.b_o = self.slopes = self.sink = self.blend_weight = None
+        self.magnitude = 1.0
         # the kernels of grouped attention take equal key and value sizes: any up to 256 in float32, multiples of 16 in bfloat16;
         # a distance bias and kept first keys are known to the kernels that take two sizes
         self.plain_kernels = (spec.v_head_dim == spec.head_dim and (dtype == torch.float32 or spec.head_dim % 16 == 0)
-                              and spec.distance_slopes is None and not spec.keep_first)
+                              and spec.distance_slopes is None and not spec.keep_first and spec.fixed_sink is None)
 
     def _widths(self):
         s = self.spec
@@ -61,6 +90,8 @@ class GatedAttention(Mixer):
         rows = {s.q_name: q, s.k_name: k, s.v_name: v, s.gate: o}
         out = {p + n: ParamSpec((rows[n], s.hidden)) for n in self._in_names()}
         out[p + s.o_name] = ParamSpec((s.hidden, o))
+        if s.value_blend is not None:
+            out[p + s.value_blend] = ParamSpec((), init="normal")
         if s.bias:
             out.update({p + n + s.bias_suffix: ParamSpec((rows[n],), init="normal") for n in self._in_names() if n != s.gate})
             out[p + s.o_name + s.bias_suffix] = ParamSpec((s.hidden,), init="normal")
@@ -85,6 +116,10 @@ class GatedAttention(Mixer):
             self.b_o = get(p + s.o_name + s.bias_suffix)
         if s.distance_slopes is not None:
             self.slopes = torch.tensor(s.distance_slopes, dtype=torch.float32, device=self.device)
+        if s.fixed_sink is not None:
+            self.sink = torch.full((s.n_heads,), float(s.fixed_sink), dtype=torch.float32, device=self.device)
+        if s.value_blend is not None:
+            self.blend_weight = get(p + s.value_blend)
 
     def prepare(self, max_positions):
         from ..ops.library import for_head_dim, gated, mixers
@@ -98,9 +133,13 @@ class GatedAttention(Mixer):
             for_head_dim(self.spec.head_dim)
         if isinstance(self.spec.position, RotaryPairsSpec):
             self.freq = pair_frequencies(self.spec.position, self.device)
+        elif isinstance(self.spec.position, RotaryHalvesSpec):
+            self.freq, self.magnitude = halves_frequencies(self.spec.position, self.device)
+            if not self.spec.position.dims:
+                self.freq = None
 
     def weights(self):
-        return [t for t in (self.w_in, self.w_o, self.b_in, self.b_o) if t is not None]
+        return [t for t in (self.w_in, self.w_o, self.b_in, self.b_o, self.blend_weight) if t is not None]
 
     def cache_needs(self):
         s = self.spec
@@ -121,9 +160,21 @@ class GatedAttention(Mixer):
             proj = linear(h if h is not None else x_norm[1].forward(x_norm[0], ctx.dtype), self.w_in, self.b_in, out_dtype=ctx.dtype)
         else:
             proj = first_product(*normed_rows(h, x_norm, ctx, self.w_in), self.w_in, ctx)
-        rot_dims = s.position.dims if isinstance(s.position, RotaryPairsSpec) else 0
+        rot_dims = s.position.dims if isinstance(s.position, (RotaryPairsSpec, RotaryHalvesSpec)) else 0
         n_kv = s.n_kv_heads if s.own_kv else 0             # a row of proj then has no key and value entries
-        if rot_dims or s.qk_unit_norm or owns_cache:
+        if isinstance(s.position, RotaryHalvesSpec):
+            blend_key = "value_blend:" + s.value_blend_key
+            blend = None
+            if s.value_blend_role == "reader":
+                blend = ctx.scratch.get(blend_key)
+                if blend is None:
+                    raise ConfigError(f"{s.prefix}: no earlier mixer of this step has shown the values it blends with")
+            kernels.rotary_half_store(proj, s.n_heads, n_kv, s.head_dim, s.v_head_dim, self.freq, rot_dims, self.magnitude, s.qk_unit_norm,
+                                      s.norm_eps, ctx.tok_pos, ctx.tok_row, kv.k if owns_cache else None, kv.v if owns_cache else None,
+                                      kv.table if owns_cache else None, kv.stride, blend, self.blend_weight if blend is not None else None)
+            if s.value_blend_role == "source":             # this step's values, as they lie in the product's rows
+                ctx.scratch[blend_key] = proj[:, q_w + k_w: q_w + k_w + v_w]
+        elif rot_dims or s.qk_unit_norm or owns_cache:
             kernels.rotary_norm_store(proj, s.n_heads, n_kv, s.head_dim, s.v_head_dim, self.freq, rot_dims, s.qk_unit_norm,
                                       s.norm_eps, ctx.tok_pos, ctx.tok_row, kv.k if owns_cache else None, kv.v if owns_cache else None,
                                       kv.table if owns_cache else None, kv.stride)
@@ -132,7 +183,7 @@ class GatedAttention(Mixer):
                                   ctx.tok_pos, ctx.tok_row, s.window, s.scale, ctx, own_rows_only=owns_cache)
         else:
             a = kernels.attention_headmix(proj, proj.shape[1], s.n_heads, s.n_kv_heads, s.head_dim, s.v_head_dim, kv.k, kv.v,
-                                          kv.table, kv.stride, ctx.tok_pos, ctx.tok_row, s.window, s.scale, None, None, ctx,
+                                          kv.table, kv.stride, ctx.tok_pos, ctx.tok_row, s.window, s.scale, self.sink, None, ctx,
                                           slopes=self.slopes, keep_first=s.keep_first)
         if s.gate is None:
             return a

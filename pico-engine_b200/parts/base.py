@@ -14,7 +14,8 @@ attention part does so for a schedule entry that reads another entry's cache (``
 Interfaces
 ----------
 Norm          ``forward(x_f32 [T,H], out_dtype, rows_index=None) -> [rows,H]``; optionally
-              ``add_forward(x, y, out_dtype)``: x += y and the norm in one pass
+              ``add_forward(x, y, out_dtype)``: x += y and the norm in one pass; ``add_into(x, y, then, out_dtype)``:
+              x += norm(y), and the next norm of x, in one pass
 Position      ``prepare(max_positions)``; ``rotate_and_store(qkv, n_q, n_kv, head_dim, ctx, kv)``
 Mixer         ``cache_needs()``; ``prepare(max_positions)``; ``apply(h, ctx, entry, cache_entry,
               owns_cache) -> y``; optionally ``add_to(x, norm, ctx, ...)`` fused
@@ -80,26 +81,41 @@ class StepContext:
     max_context: int = 0                  # upper bound of any row's length after the step
     scratch: Dict[str, torch.Tensor] = field(default_factory=dict)   # named buffers that live as long as the step
     pending: Optional[torch.Tensor] = None  # a product [T, hidden] that still has to be added to the residual stream
+    pending_norm: Optional["Norm"] = None   # the norm that product passes on its way into the stream (None: it is added as it is)
 
     # A part whose product comes out of the library may leave the sum into the residual stream pending, so
     # that the norm that follows does both in one pass.  Whoever reads the stream first settles it: parts
-    # that declare ``takes_pending`` through ``normed``, everyone else through the arrangement.
+    # that declare ``takes_pending`` through ``normed``, everyone else through the arrangement.  A sublayer's
+    # output that is normed before it is added (``defer_normed_add``) waits the same way: that norm, the sum and
+    # the next reader's norm are then one pass over the rows.
     def defer_add(self, x: torch.Tensor, y: torch.Tensor) -> None:
         self.settle(x)
         self.pending = y
 
+    def defer_normed_add(self, x: torch.Tensor, y: torch.Tensor, norm: "Norm") -> None:
+        """x += norm(y), left pending."""
+        self.settle(x)
+        self.pending, self.pending_norm = y, norm
+
     def settle(self, x: torch.Tensor) -> None:
         if self.pending is not None:
             from ..ops import kernels
-            y, self.pending = self.pending, None
-            kernels.residual_add(x, y.contiguous())
+            y, n = self.pending, self.pending_norm
+            self.pending = self.pending_norm = None
+            if n is None:
+                kernels.residual_add(x, y.contiguous())
+            else:
+                n.add_into(x, y.contiguous())
 
     def normed(self, x: torch.Tensor, norm: "Norm") -> torch.Tensor:
         """norm(x) in the step's dtype, after what is pending has been added to x."""
         if self.pending is None:
             return norm.forward(x, self.dtype)
-        y, self.pending = self.pending, None
-        return norm.add_forward(x, y.contiguous(), self.dtype)
+        y, n = self.pending, self.pending_norm
+        self.pending = self.pending_norm = None
+        if n is None:
+            return norm.add_forward(x, y.contiguous(), self.dtype)
+        return n.add_into(x, y.contiguous(), then=norm, out_dtype=self.dtype)
 
     def kv(self, cache_entry: int) -> KVView:
         g = self.cache.group_of[cache_entry]
@@ -171,6 +187,13 @@ class Norm(Part):
         from ..ops import kernels
         kernels.residual_add(x, y)
         return self.forward(x, out_dtype)
+
+    def add_into(self, x: torch.Tensor, y: torch.Tensor, then: Optional["Norm"] = None, out_dtype: Optional[torch.dtype] = None):
+        """x += forward(y) in place on the float32 stream (y: a sublayer's output, float32 or the step's dtype); with ``then`` also
+        returns then.forward(x) of the rows as they then stand.  Norms override this to do all of it in one pass."""
+        from ..ops import kernels
+        kernels.residual_add(x, self.forward(y if y.dtype == torch.float32 else y.float(), torch.float32))
+        return None if then is None else then.forward(x, out_dtype)
 
 
 class Position(Part):

@@ -66,6 +66,8 @@ class Layer:
         self.feed_forward_norm = build(NORMS, "norm", spec.feed_forward_norm) or PassThrough(dtype, device)
         self.mixer_input = build(INPUT_FILTERS, "input filter", spec.mixer_input)
         self.feed_forward_input = build(INPUT_FILTERS, "input filter", spec.feed_forward_input)
+        self.mixer_out_norm = build(NORMS, "norm", spec.mixer_out_norm)
+        self.feed_forward_out_norm = build(NORMS, "norm", spec.feed_forward_out_norm)
         self.mixer_scale = None if spec.mixer_scale is None else ScaleVector(spec.mixer_scale, _hidden_of(spec), dtype, device)
         self.feed_forward_scale = None if spec.feed_forward_scale is None else \
             ScaleVector(spec.feed_forward_scale, _hidden_of(spec), dtype, device)
@@ -79,7 +81,8 @@ class Layer:
     def parts(self):
         """The parts that are there (a stand-in for an absent norm has no tensors and is left out)."""
         return tuple(p for p in (self.mixer, self.mixer_norm, self.mixer_input, self.feed_forward, self.feed_forward_norm,
-                                 self.feed_forward_input, self.mixer_scale, self.feed_forward_scale)
+                                 self.feed_forward_input, self.mixer_scale, self.feed_forward_scale, self.mixer_out_norm,
+                                 self.feed_forward_out_norm)
                      if p is not None and not isinstance(p, PassThrough))
 
     def cache_needs(self):
@@ -201,3 +204,20 @@ def post_norm(layer: Layer, x, ctx, entry, cache_entry, owns_cache) -> None:
             y = y.float()
         kernels.normed_sum_add(x, [y.contiguous()], [norm.weight.float().contiguous() if scale is None else scale.times(norm.weight)],
                                norm.eps, 1.0)
+
+
+@register_arrangement("sandwich")
+def sandwich(layer: Layer, x, ctx, entry, cache_entry, owns_cache) -> None:
+    """x += out_norm1(mixer(norm1(x))); x += out_norm2(feed_forward(norm2(x))): a norm before and one after each sublayer.  A
+    sublayer hands over the float32 sums of its last product where it can; its output norm and the sum into the stream are left
+    pending, so that they and the norm in front of whatever reads the stream next are one kernel in float32."""
+    halves = ((layer.mixer, layer.mixer_norm, layer.mixer_out_norm, (entry, cache_entry, owns_cache)),
+              (layer.feed_forward, layer.feed_forward_norm, layer.feed_forward_out_norm, ()))
+    for part, norm, out_norm, where in halves:
+        if part is None:
+            continue
+        if out_norm is None:
+            raise ConfigError("the sandwich arrangement takes a norm on every sublayer's output")
+        h = ctx.normed(x, norm)
+        extra = {"out_dtype": x.dtype} if getattr(part, "takes_out_dtype", False) else {}
+        ctx.defer_normed_add(x, part.apply(h, ctx, *where, **extra), out_norm)

@@ -86,14 +86,16 @@ class DenseMLP(FeedForward):
 @register_feed_forward(GatedMLPSpec)
 class GatedMLP(FeedForward):
     """down(act(gate(h)) * up(h)) without biases, gate and up as one product on concatenated weights; act is gelu
-    (tanh formula) or silu, and act(gate) * up is formed in float32."""
+    (tanh formula) or silu, or the clamped form min(gate, l) sigmoid(a min(gate, l)) (clamp(up, -l, l) + 1); formed in float32."""
 
     takes_out_dtype = True      # apply(..., out_dtype=) gives the product's float32 sums where the caller goes on in float32
 
     def __init__(self, spec: GatedMLPSpec, dtype, device):
         super().__init__(spec, dtype, device)
-        if spec.activation not in ("gelu_tanh", "silu"):
-            raise ConfigError(f"activation {spec.activation!r} is not known; known: gelu_tanh, silu")
+        if spec.activation not in ("gelu_tanh", "silu", "clamped_sigmoid"):
+            raise ConfigError(f"activation {spec.activation!r} is not known; known: gelu_tanh, silu, clamped_sigmoid")
+        if spec.activation == "clamped_sigmoid" and not (spec.limit is not None and spec.limit > 0):
+            raise ConfigError(f"the clamped activation needs a positive limit, found {spec.limit!r}")
         self.w_gate_up = self.w_down = None
 
     def expected_tensors(self):
@@ -115,7 +117,7 @@ class GatedMLP(FeedForward):
             from ..ops.linear import gate_up_swiglu
             return gate_up_swiglu(h, self.w_gate_up)
         gate_up = first_product(*normed_rows(h, x_norm, ctx, self.w_gate_up), self.w_gate_up, ctx)
-        return kernels.gated_act(gate_up, self.spec.activation)
+        return kernels.gated_act(gate_up, self.spec.activation, limit=self.spec.limit or 0.0, alpha=self.spec.alpha)
 
     def apply(self, h, ctx, out_dtype=None):
         return linear(self._activation(h, ctx), self.w_down, out_dtype=out_dtype or ctx.dtype)

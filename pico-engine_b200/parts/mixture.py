@@ -12,7 +12,8 @@ from .base import FeedForward, first_product, last_product_into, normed_rows, re
 @register_feed_forward(MixtureSpec)
 class Mixture(FeedForward):
     """Every token uses the ``top_k`` experts with the largest router logits, weighted by the softmax over those logits;
-    a shared expert runs for every token, times one sigmoid gate.  Router and shared gate are one float32 product (their
+    a shared expert runs for every token, times one sigmoid gate.  With sigmoid scores the choice reads score + a stored correction
+    among the best groups of neighbouring experts, and the weights are the chosen experts' plain scores (``kernels.moe_route_grouped``).  Router and shared gate are one float32 product (their
     weights are kept in float32), the choice and the weights one kernel (csrc/gated_ops.cu: dense weights [T, experts + 1],
     zero for experts a token does not use).
 
@@ -32,9 +33,18 @@ class Mixture(FeedForward):
             raise ConfigError(f"top_k = {spec.top_k} must lie in 1 .. n_experts = {spec.n_experts}")
         if spec.activation not in kernels.GATE_ACTIVATIONS:
             raise ConfigError(f"activation {spec.activation!r} is not known")
-        if spec.scores not in ("softmax_chosen", "softmax_all"):
-            raise ConfigError(f"scores must be \"softmax_chosen\" or \"softmax_all\", not {spec.scores!r}")
-        self.w_router = self.w_gate_up = self.w_down = None
+        if spec.scores not in ("softmax_chosen", "softmax_all", "sigmoid"):
+            raise ConfigError(f"scores must be \"softmax_chosen\", \"softmax_all\" or \"sigmoid\", not {spec.scores!r}")
+        if spec.scores == "sigmoid":
+            if spec.shared_intermediate is not None:
+                raise ConfigError("sigmoid scores come without a shared expert")
+            per = spec.n_experts // max(spec.n_groups, 1)
+            if (spec.n_groups < 1 or spec.n_experts % spec.n_groups or not 1 <= spec.keep_groups <= spec.n_groups
+                    or spec.keep_groups * per < spec.top_k or spec.group_best < 1):
+                raise ConfigError(f"{spec.n_experts} experts in {spec.n_groups} groups of which {spec.keep_groups} stay cannot give {spec.top_k}")
+        elif spec.correction_name is not None or spec.n_groups != 1:
+            raise ConfigError("a correction and groups of experts belong to sigmoid scores")
+        self.w_router = self.w_gate_up = self.w_down = self.correction = None
 
     def _experts(self):
         s = self.spec
@@ -59,6 +69,8 @@ class Mixture(FeedForward):
             out.update({p + s.up_name: ParamSpec((ff, s.hidden)), p + s.down_name: ParamSpec((s.hidden, ff))})
         if self._shared_gate():
             out[s.prefix + s.shared_gate_name] = ParamSpec((1, s.hidden))
+        if s.correction_name is not None:
+            out[s.prefix + s.correction_name] = ParamSpec((s.n_experts,))
         return out
 
     def take_tensors(self, get):
@@ -69,6 +81,8 @@ class Mixture(FeedForward):
         gates = [get(p + s.gate_name) for p, _ in experts] if s.gated else []
         self.w_gate_up = torch.cat(gates + [get(p + s.up_name) for p, _ in experts], dim=0).contiguous()
         self.w_down = torch.cat([get(p + s.down_name) for p, _ in experts], dim=1).contiguous()
+        if s.correction_name is not None:
+            self.correction = get(s.prefix + s.correction_name).float().contiguous()
 
     def prepare(self, max_positions):
         from ..ops.library import gated
@@ -78,6 +92,9 @@ class Mixture(FeedForward):
         """Dense weights float32 [T, n_experts (+ 1)] of rows h."""
         s = self.spec
         logits = linear(h, self.w_router, out_dtype=torch.float32)
+        if s.scores == "sigmoid":
+            return kernels.moe_route_grouped(logits, s.n_experts, s.top_k, self.correction, s.n_groups, s.keep_groups, s.group_best,
+                                             s.route_scale)
         return kernels.moe_route(logits, s.n_experts, s.top_k, self._extra(), over_all=s.scores == "softmax_all", factor=s.route_scale)
 
     def _activation(self, h, ctx, x_norm=None):
@@ -85,7 +102,8 @@ class Mixture(FeedForward):
         from .block import PassThrough
         from .norm import RMSNorm
         how = {"over_all": s.scores == "softmax_all", "factor": s.route_scale}
-        if x_norm is not None and type(x_norm[1]) in (RMSNorm, PassThrough) and s.n_experts <= kernels.MOE_ROUTE_STREAM_MAX_EXPERTS:
+        if (x_norm is not None and type(x_norm[1]) in (RMSNorm, PassThrough) and s.n_experts <= kernels.MOE_ROUTE_STREAM_MAX_EXPERTS
+                and s.scores != "sigmoid"):
             # the router reads the float32 stream itself (its norm, where it has one, is part of the routing kernel): the same
             # logits however the step is cut, and the gate/up product may take the norm into its prologue
             x, norm = x_norm

@@ -79,7 +79,7 @@ class DecoderModel:
         """The residual stream [T, hidden] float32 after the last layer."""
         pairs = self.plan.embedding_pairs
         if pairs is None:
-            x = kernels.embed(self.embedding, token_ids)
+            x = kernels.embed(self.embedding, token_ids, scale=self.plan.embedding_scale)
         else:
             x = kernels.embed_pairs(self.embedding, self.pair_table, token_ids, ctx.tok_pos, ctx.tok_row, ctx.row_first, ctx.slots,
                                     ctx.state(len(self.plan.schedule)), pairs.buckets, pairs.mul_prev, pairs.mul_cur)

@@ -55,3 +55,12 @@ class LayerNorm(Norm):
 
     def forward(self, x, out_dtype, rows_index=None):
         return kernels.layernorm(x, self.weight, self.bias, self.eps, out_dtype, rows_index)
+
+    def add_into(self, x, y, then=None, out_dtype=None):
+        """x += layernorm(y); with a layer norm ``then`` its rows of the new x come out of the same kernel."""
+        if then is None:
+            return kernels.layernorm_add(x, y, self.weight, self.bias, self.eps)
+        if type(then) is LayerNorm:
+            return kernels.layernorm_add(x, y, self.weight, self.bias, self.eps, (then.weight, then.bias, then.eps), out_dtype)
+        kernels.layernorm_add(x, y, self.weight, self.bias, self.eps)
+        return then.forward(x, out_dtype)
