@@ -863,6 +863,7 @@ __global__ void __launch_bounds__(128) moe_route_grouped_kernel(const float* log
     float* c = s_c[wi];
     float* gs = s_g[wi];
     float* w = weights + (size_t)t * E;
+    if (ids) ids += (size_t)t * top;
     for (int e = lane; e < E; e += 32) {
         c[e] = go_sigmoid(z[e]) + (corr ? load_as_f(corr, corr_dtype, e) : 0.f);
         w[e] = 0.f;

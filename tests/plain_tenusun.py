@@ -168,6 +168,9 @@ def dense_ff(h, mlp, w, p):
     return lin(w[p + "down"], g * sigmoid(1.702 * g) * (u + 1))
 
 
+ROUTER_GAPS = None      # a list: every call of ``route`` appends, a token, by how little its choice was made (for the tests)
+
+
 def route(h, mlp, w, p):
     """[(expert, weight)] a token.  Scores are sigmoids of the router's logits; the choice reads score + correction, first among
     groups of neighbouring experts (a group counts the sum of its two largest; only the best ``keep`` groups stay), then the
@@ -177,9 +180,10 @@ def route(h, mlp, w, p):
     s = sigmoid(lin(w[p + "router"].to(h.dtype), h))
     choice = s + w[p + "correction"].to(h.dtype)
     groups = r.get("groups")
-    out = []
+    out, gaps = [], []
     for t in range(h.shape[0]):
         c = choice[t].clone()
+        gap = math.inf
         if groups is not None and groups["count"] > 1:
             per = E // groups["count"]
             totals = []
@@ -187,10 +191,17 @@ def route(h, mlp, w, p):
                 best = torch.sort(c[g * per:(g + 1) * per], descending=True).values
                 totals.append(float(best[:2].sum()))
             order = sorted(range(groups["count"]), key=lambda g: (-totals[g], g))
+            if groups["keep"] < groups["count"]:
+                gap = totals[order[groups["keep"] - 1]] - totals[order[groups["keep"]]]
             for g in order[groups["keep"]:]:
                 c[g * per:(g + 1) * per] = -math.inf
-        chosen = sorted(range(E), key=lambda e: (-float(c[e]), e))[:top]
-        out.append([(e, s[t, e]) for e in chosen])
+        ranked = sorted(range(E), key=lambda e: (-float(c[e]), e))
+        if top < E and c[ranked[top]] > -math.inf:
+            gap = min(gap, float(c[ranked[top - 1]] - c[ranked[top]]))
+        gaps.append(gap)
+        out.append([(e, s[t, e]) for e in ranked[:top]])
+    if ROUTER_GAPS is not None:
+        ROUTER_GAPS.append(torch.tensor(gaps))
     return out
 
 
