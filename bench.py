@@ -62,7 +62,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (recorded in config)")
-    ap.add_argument("--design", default=None, choices=["mebalorn", "kevelorn", "pupidra"],
+    ap.add_argument("--design", default=None, choices=["mebalorn", "kevelorn", "pupidra", "tenusun"],
                     help="instead of the default workload: prefill and decode throughput of this design at a few layer sizes "
                          "beside the Qwen2 decoder at equal widths, and its kernels beside the like Qwen2 kernels")
     ap.add_argument("--sizes", default="s,m", help="with --design: which of the sizes s, m, l")

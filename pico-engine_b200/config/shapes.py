@@ -1,5 +1,5 @@
 """config.json contents of the shapes the benchmarks and tests name: the two tiny test
-configurations, the Qwen2.5 sizes and Mebalorn, Kevelorn and Pupidra models at the same widths (weights for them are drawn at random)."""
+configurations, the Qwen2.5 sizes and Mebalorn, Kevelorn, Pupidra and Tenusun models at the same widths (weights for them are drawn at random)."""
 from __future__ import annotations
 
 _QWEN2 = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", "torch_dtype": "bfloat16"}
@@ -104,6 +104,33 @@ SHAPES.update({
     "pupidra-tiny": pupidra_shape(64, 4, 2, 16, 160, 4, 256, window=40, keep_first=3, experts=4, state=24, buckets=97),
     "pupidra-0.5b": pupidra_shape(896, 14, 2, 64, 4864, 24, 151936),            # the widths of qwen2.5-0.5b
     "pupidra-7b": pupidra_shape(3584, 28, 4, 128, 18944, 28, 152064),           # the widths of qwen2.5-7b
+})
+
+
+def tenusun_shape(width: int, heads: int, kv_heads: int, dim: int, ff: int, layers: int, vocab: int, window: int = 1024,
+                  experts: int = 8, top: int = 2, groups=(4, 2), vdim: int | None = None) -> dict:
+    """A Tenusun config.json whose layers take these two forms in turn: latent attention behind a sliding window (a cached row of at
+    most 256 entries: rank 2 dim or 256 - dim / 2, rotated part dim / 2, a query row a quarter of the width) with the dense clamped
+    feed-forward, and grouped attention (half of a head rotated, stretched eightfold; values blended from the second such layer on)
+    with a mixture whose experts are a quarter as wide as the dense feed-forward."""
+    rot = max(2, dim // 2)
+    rank = min(2 * dim, 256 - rot)
+    lat = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "kv_rank": rank, "q_rank": max(64, width // 4 // 64 * 64),
+           "scale": (dim + rot) ** -0.5, "rot": {"base": 250000.0, "dims": rot}, "mask": {"size": window}}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim or dim, "scale": dim ** -0.5, "v_mix": True,
+           "rot": {"base": 250000.0, "dims": rot, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top, "groups": {"count": groups[0], "keep": groups[1]}}, "expert": {"ff": ff // 4}}
+    out = [{"type": "latent_attention", "mixer": dict(lat), "mlp": dict(dense)} if i % 2 == 0 else
+           {"type": "attention", "mixer": dict(att), "mlp": dict(moe)} for i in range(layers)]
+    return {"architecture": "Tenusun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": float(width) ** 0.5},
+            "layers": out}
+
+
+SHAPES.update({
+    "tenusun-tiny": tenusun_shape(64, 4, 2, 16, 160, 4, 256, window=40, experts=4, groups=(2, 1), vdim=8),
+    "tenusun-0.5b": tenusun_shape(896, 14, 2, 64, 4864, 24, 151936),            # the widths of qwen2.5-0.5b
+    "tenusun-7b": tenusun_shape(3584, 28, 4, 128, 18944, 28, 152064),           # the widths of qwen2.5-7b
 })
 
 

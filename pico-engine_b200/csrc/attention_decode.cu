@@ -224,7 +224,7 @@ __global__ void __launch_bounds__(32 * (AD_WARPS + 1), AD_CTAS(AD_WARPS)) attent
     const bf16* q, int q_stride, const bf16* k_pool, const bf16* v_pool,
     const int* block_table, int table_stride, const int* tok_pos,
     const int* tok_row, int nh, int nkv, int window, float scale_log2e, int n_splits, int stages,
-    int* status, bf16* out, int keep_first, const float* slopes) {
+    int* status, bf16* out, int keep_first, const float* slopes, const float* sinks) {
     constexpr int AD_GROUPS = AD_WARPS / 4, AD_THREADS = 32 * (AD_WARPS + 1);
     extern __shared__ __align__(128) unsigned char ad_smem[];   // result rows, then the ring (later: the warps' partial results)
     __shared__ __align__(8) unsigned long long bars[2 * AD_MAX_STAGES + 1];
@@ -424,6 +424,8 @@ __global__ void __launch_bounds__(32 * (AD_WARPS + 1), AD_CTAS(AD_WARPS)) attent
             l += w_sum[w * 16 + row];
         }
         if (n_splits == 1) {
+            // sinks [nh] (or null): one more place of that score joins the head's denominator and carries no value
+            if (sinks) l += exp2f(fmaf(sinks[kvh * G + ht * 16 + row], 1.4426950408889634f, -m));
             out[((size_t)tok * nh + kvh * G + ht * 16 + row) * AD_HD + col] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
             continue;
         }
@@ -462,6 +464,7 @@ __global__ void __launch_bounds__(32 * (AD_WARPS + 1), AD_CTAS(AD_WARPS)) attent
             o = fmaf(src[j], wgt, o);
             l = fmaf(src[slice + 1], wgt, l);
         }
+        if (sinks) l += exp2f(fmaf(sinks[kvh * G + ht * 16 + row], 1.4426950408889634f, -m));
         out[((size_t)tok * nh + kvh * G + ht * 16 + row) * AD_HD + split * slice + j] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
     }
 }
@@ -550,7 +553,7 @@ struct AdVariant {
     static int launch(dim3 grid, int n_splits, int stages, cudaStream_t stream, const bf16* q, int q_stride, const bf16* k_pool,
                       const bf16* v_pool, const int* block_table, int table_stride, const int* tok_pos, const int* tok_row,
                       int nh, int nkv, int window, float scale_log2e, int* status, bf16* out, bool early, int keep_first,
-                      const float* slopes) {
+                      const float* slopes, const float* sinks) {
         const size_t smem = smem_bytes(stages);
         { const int e = allow_smem(smem); if (e) return e; }
         cudaLaunchConfig_t cfg = {};
@@ -573,7 +576,7 @@ struct AdVariant {
         cfg.attrs = attr;
         cfg.numAttrs = n_attr;
         PE_TRY(cudaLaunchKernelEx(&cfg, attention_decode_kernel<WARPS>, q, q_stride, k_pool, v_pool, block_table, table_stride,
-                                  tok_pos, tok_row, nh, nkv, window, scale_log2e, n_splits, stages, status, out, keep_first, slopes));
+                                  tok_pos, tok_row, nh, nkv, window, scale_log2e, n_splits, stages, status, out, keep_first, slopes, sinks));
         PE_LAUNCH_CHECK();
         return 0;
     }
@@ -612,9 +615,10 @@ extern "C" int pe_attention_decode_splits(int T, int nh, int nkv, int max_contex
 extern "C" int pe_attention_decode(const void* q, int q_stride, void* out, const void* k_pool, const void* v_pool,
                                    const int* block_table, int table_stride, const int* tok_pos, const int* tok_row,
                                    int T, int nh, int nkv, int hd, int window, float scale, int max_context,
-                                   int early_pages, int* status, void* stream, int keep_first, const float* slopes) {
+                                   int early_pages, int* status, void* stream, int keep_first, const float* slopes, const float* sinks) {
     // keep_first: with a window, a sequence's first so many keys stay visible.  slopes [nh] float32 (or null):
-    // slope_h * (position - key) is taken off the scaled score.
+    // slope_h * (position - key) is taken off the scaled score.  sinks [nh] float32 (or null): one more place of score sinks[h]
+    // joins the softmax denominator of head h and carries no value.
     // early_pages 1: the kernel may start while the kernels before it in the stream still run, and copies cache pages
     // at once; those kernels (the one before it, and the one before that, which it can overlap too) must then have
     // written no cache row but each token's own (which is fetched again after the wait).  0: it starts when they have ended.
@@ -633,9 +637,9 @@ extern "C" int pe_attention_decode(const void* q, int q_stride, void* out, const
         if (wide)
             return AdVariant<16>::launch(grid, n_splits, stages, (cudaStream_t)stream, (const bf16*)q, q_stride, (const bf16*)k_pool,
                                          (const bf16*)v_pool, block_table, table_stride, tok_pos, tok_row, nh, nkv, window,
-                                         scale_log2e, status, (bf16*)out, early_pages != 0, keep_first, slopes);
+                                         scale_log2e, status, (bf16*)out, early_pages != 0, keep_first, slopes, sinks);
     }
     return AdVariant<8>::launch(grid, n_splits, stages, (cudaStream_t)stream, (const bf16*)q, q_stride, (const bf16*)k_pool,
                                 (const bf16*)v_pool, block_table, table_stride, tok_pos, tok_row, nh, nkv, window, scale_log2e,
-                                status, (bf16*)out, early_pages != 0, keep_first, slopes);
+                                status, (bf16*)out, early_pages != 0, keep_first, slopes, sinks);
 }

@@ -58,6 +58,7 @@ struct AtArgs {
     int keep_first;                                // with a window: the first so many keys of a sequence stay visible
     const float* slopes; float inv_scale;          // [nh] or null: slopes[h] * (query position - key position) is taken off the scaled score
     int pool_rows;                                 // rows of the key (and value) pool seen as a matrix [rows][head size]
+    const float* sinks;                            // [nh] or null: one more place of this (scaled) score joins a row's denominator and carries no value
 };
 
 __device__ __forceinline__ unsigned at_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -407,7 +408,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tcgen05_kerne
         if (ok && it > 0 && !at_wait_warp(at_smem(&pv_done[(it - 1) & 1]), (unsigned)((it - 1) >> 1) & 1u)) ok = false;
         if (ok && it > 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float l = g == 0 ? l_run + l_theirs : l_theirs + l_run;   // the same sum in both threads
+            float l = g == 0 ? l_run + l_theirs : l_theirs + l_run;         // the same sum in both threads
+            if (p.sinks) l += at_exp2(fmaf(p.sinks[h], 1.4426950408889634f, -m_run));   // (a row that saw no key: 2^inf, and 1 / l = 0)
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             bf16* o_row = p.out + ((size_t)(tok0 + r) * p.nh + h) * AT_HD + g * (AT_HD / 2);
 #pragma unroll 1
@@ -480,7 +482,7 @@ extern "C" int pe_attention_prefill_tcgen05_ctas_per_sm() {
 extern "C" int pe_attention_prefill_tcgen05(const void* q, int q_stride, void* out, const void* k_pool, const void* v_pool,
                                             long long pool_pages, const int* block_table, int table_stride, const void* tiles,
                                             int n_tiles, int n_tokens, int nh, int nkv, int hd, int window, float scale,
-                                            int keep_first, const float* slopes, int* status, void* stream) {
+                                            int keep_first, const float* slopes, int* status, void* stream, const float* sinks) {
     if (n_tiles <= 0) return 0;
     if (hd != AT_HD || nkv <= 0 || nh % nkv || n_tiles > 65535 || q_stride % 8 || !(scale > 0.f) || !status) return PE_ERR_UNSUPPORTED;
     if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out | (uintptr_t)tiles) & 15) return PE_ERR_UNSUPPORTED;
@@ -497,6 +499,7 @@ extern "C" int pe_attention_prefill_tcgen05(const void* q, int q_stride, void* o
     p.nh = nh; p.nkv = nkv; p.window = window; p.scale_log2e = scale * 1.4426950408889634f;
     p.keep_first = window > 0 && keep_first > 0 ? keep_first : 0; p.slopes = slopes; p.inv_scale = 1.0f / scale;
     p.pool_rows = (int)(pool_pages * nkv * AT_KTILE);
+    p.sinks = sinks;
     const size_t smem = AT_SMEM_BYTES;
     static bool attr_set = false;
     if (!attr_set) {
@@ -512,7 +515,7 @@ extern "C" int pe_attention_prefill_tcgen05(const void* q, int q_stride, void* o
 extern "C" int pe_attention_prefill_tcgen05_tile() { return 0; }
 extern "C" int pe_attention_prefill_tcgen05_ctas_per_sm() { return 0; }
 extern "C" int pe_attention_prefill_tcgen05(const void*, int, void*, const void*, const void*, long long, const int*, int, const void*,
-                                            int, int, int, int, int, int, float, int, const float*, int*, void*) {
+                                            int, int, int, int, int, int, float, int, const float*, int*, void*, const float*) {
     return PE_ERR_UNSUPPORTED;
 }
 

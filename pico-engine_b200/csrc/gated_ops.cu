@@ -587,6 +587,11 @@ __global__ void gated_act_bf16x8_kernel(const bf16* gu, bf16* out, int I, int ac
     const int per_row = I / 8;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < units; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / per_row, c = (idx % per_row) * 8;
+        if (colw && (group & 7) == 0 && colw[t * n_groups + min((int)(c / group), n_groups - 1)] == 0.f) {
+            // eight columns of an expert the token does not use: exact zeros, and its hidden units are not read
+            *reinterpret_cast<uint4*>(out + t * I + c) = make_uint4(0u, 0u, 0u, 0u);
+            continue;
+        }
         const uint4 g = *reinterpret_cast<const uint4*>(gu + t * 2 * I + c), u = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + c);
         const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
         const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
@@ -849,21 +854,9 @@ extern "C" int pe_moe_route(const float* logits, int ld, int E, int top, int ext
 // ids [T, top] int32 (or null) receives the chosen experts, largest c first.  A warp a token, four tokens a block.
 #define MG_MAX_E 1024
 #define MG_MAX_GROUPS 64
-__global__ void __launch_bounds__(128) moe_route_grouped_kernel(const float* logits, int ld, int E, int top, const void* corr, int corr_dtype,
-                                                                int n_groups, int keep, int group_best, float factor, float* weights,
-                                                                int* ids, int T) {
-    pdl_launch_dependents();
-    __shared__ float s_c[4][MG_MAX_E];
-    __shared__ float s_g[4][MG_MAX_GROUPS];
-    const int wi = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + wi;
-    pdl_wait();
-    if (t >= T) return;
-    const float* z = logits + (size_t)t * ld;
-    float* c = s_c[wi];
-    float* gs = s_g[wi];
-    float* w = weights + (size_t)t * E;
-    if (ids) ids += (size_t)t * top;
+// The choice itself, by one warp: z [E] the logits, c [E] and gs [n_groups] scratch of the warp.
+__device__ __forceinline__ void moe_choose_grouped(const float* z, float* c, float* gs, int E, int top, const void* corr, int corr_dtype,
+                                                   int n_groups, int keep, int group_best, float factor, float* w, int* ids, int lane) {
     for (int e = lane; e < E; e += 32) {
         c[e] = go_sigmoid(z[e]) + (corr ? load_as_f(corr, corr_dtype, e) : 0.f);
         w[e] = 0.f;
@@ -937,6 +930,106 @@ __global__ void __launch_bounds__(128) moe_route_grouped_kernel(const float* log
         if ((at & 31) == lane) taken |= 1ull << (at >> 5);
         if (lane == 0) { w[at] = factor * go_sigmoid(z[at]); if (ids) ids[k] = at; }
     }
+}
+
+__global__ void __launch_bounds__(128) moe_route_grouped_kernel(const float* logits, int ld, int E, int top, const void* corr, int corr_dtype,
+                                                                int n_groups, int keep, int group_best, float factor, float* weights,
+                                                                int* ids, int T) {
+    pdl_launch_dependents();
+    __shared__ float s_c[4][MG_MAX_E];
+    __shared__ float s_g[4][MG_MAX_GROUPS];
+    const int wi = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + wi;
+    pdl_wait();
+    if (t >= T) return;
+    moe_choose_grouped(logits + (size_t)t * ld, s_c[wi], s_g[wi], E, top, corr, corr_dtype, n_groups, keep, group_best, factor,
+                       weights + (size_t)t * E, ids ? ids + (size_t)t * top : nullptr, lane);
+}
+
+// The same from the float32 residual stream with the layer norm in front of the router inside the kernel: the logits are
+// router[e] . ((x - mean) / sqrt(var + eps) * norm_w + norm_b), all in float32 (var the mean of the squared deviations, two passes),
+// for up to MR_MAX_E experts.  A block a token, as in moe_route_stream_kernel: its four warps share the row, their partial sums meet
+// in shared memory in a fixed order, and the first warp chooses.
+__global__ void __launch_bounds__(MR_THREADS) moe_route_stream_grouped_kernel(const float* x, const void* norm_w, int nw_dtype, const void* norm_b,
+                                                                              int nb_dtype, float eps, const float* router, int K, int E, int top,
+                                                                              const void* corr, int corr_dtype, int n_groups, int keep,
+                                                                              int group_best, float factor, float* weights, int* ids, int T) {
+    pdl_launch_dependents();
+    __shared__ float z[MR_MAX_E];
+    __shared__ float c[MR_MAX_E];
+    __shared__ float gs[MG_MAX_GROUPS];
+    __shared__ float part[MR_THREADS / 32][8];
+    __shared__ float red[33];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t = blockIdx.x;
+    pdl_wait();
+    const float* row = x + (size_t)t * K;
+    const bool vec = K % 4 == 0 && !(((uintptr_t)x | (uintptr_t)router) & 15);
+    float s = 0.f;
+    if (vec) {
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        for (int k = tid; k < K / 4; k += MR_THREADS) { const float4 v = row4[k]; s += (v.x + v.y) + (v.z + v.w); }
+    } else {
+        for (int k = tid; k < K; k += MR_THREADS) s += row[k];
+    }
+    const float mean = block_sum(s, red) / (float)K;
+    float v2 = 0.f;
+    for (int k = tid; k < K; k += MR_THREADS) { const float d = row[k] - mean; v2 = fmaf(d, d, v2); }
+    const float rstd = 1.0f / sqrtf(block_sum(v2, red) / (float)K + eps);
+    for (int e0 = 0; e0 < E; e0 += 8) {                                     // eight logits at a time: the row is read once for them
+        float acc[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[u] = 0.f;
+        if (vec) {
+            const float4* row4 = reinterpret_cast<const float4*>(row);
+            const float4* r4 = reinterpret_cast<const float4*>(router);
+            for (int k = tid; k < K / 4; k += MR_THREADS) {
+                float4 xv = row4[k];
+                xv.x = fmaf((xv.x - mean) * rstd, load_as_f(norm_w, nw_dtype, 4 * k), load_as_f(norm_b, nb_dtype, 4 * k));
+                xv.y = fmaf((xv.y - mean) * rstd, load_as_f(norm_w, nw_dtype, 4 * k + 1), load_as_f(norm_b, nb_dtype, 4 * k + 1));
+                xv.z = fmaf((xv.z - mean) * rstd, load_as_f(norm_w, nw_dtype, 4 * k + 2), load_as_f(norm_b, nb_dtype, 4 * k + 2));
+                xv.w = fmaf((xv.w - mean) * rstd, load_as_f(norm_w, nw_dtype, 4 * k + 3), load_as_f(norm_b, nb_dtype, 4 * k + 3));
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (e0 + u < E) {
+                        const float4 r = r4[(size_t)(e0 + u) * (K / 4) + k];
+                        acc[u] = fmaf(xv.x, r.x, acc[u]); acc[u] = fmaf(xv.y, r.y, acc[u]);
+                        acc[u] = fmaf(xv.z, r.z, acc[u]); acc[u] = fmaf(xv.w, r.w, acc[u]);
+                    }
+            }
+        } else {
+            for (int k = tid; k < K; k += MR_THREADS) {
+                const float xv = fmaf((row[k] - mean) * rstd, load_as_f(norm_w, nw_dtype, k), load_as_f(norm_b, nb_dtype, k));
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (e0 + u < E) acc[u] = fmaf(xv, router[(size_t)(e0 + u) * K + k], acc[u]);
+            }
+        }
+        __syncthreads();                                                    // the sums of the eight logits before these have been read
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const float sum = warp_sum(acc[u]);
+            if (lane == 0) part[warp][u] = sum;
+        }
+        __syncthreads();
+        if (tid < 8 && e0 + tid < E) z[e0 + tid] = (part[0][tid] + part[1][tid]) + (part[2][tid] + part[3][tid]);
+    }
+    __syncthreads();
+    if (warp == 0) moe_choose_grouped(z, c, gs, E, top, corr, corr_dtype, n_groups, keep, group_best, factor, weights + (size_t)t * E,
+                                      ids ? ids + (size_t)t * top : nullptr, lane);
+}
+
+extern "C" int pe_moe_route_stream_grouped(const float* x, const void* norm_w, int nw_dtype, const void* norm_b, int nb_dtype, float eps,
+                                           const float* router, int K, int E, int top, const void* corr, int corr_dtype, int n_groups, int keep,
+                                           int group_best, float factor, float* weights, int* ids, int T, void* stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || E > MR_MAX_E || top <= 0 || top > E || K <= 0 || !norm_w || !norm_b || n_groups <= 0 || n_groups > MG_MAX_GROUPS || E % n_groups ||
+        keep <= 0 || keep > n_groups || group_best <= 0)
+        return PE_ERR_UNSUPPORTED;
+    PE_TRY(pe_launch(moe_route_stream_grouped_kernel, T, MR_THREADS, 0, (cudaStream_t)stream, x, norm_w, nw_dtype, norm_b, nb_dtype, eps, router, K,
+                     E, top, corr, corr_dtype, n_groups, keep, group_best, factor, weights, ids, T));
+    PE_LAUNCH_CHECK();
+    return 0;
 }
 
 extern "C" int pe_moe_route_grouped(const float* logits, int ld, int E, int top, const void* corr, int corr_dtype, int n_groups, int keep,

@@ -354,6 +354,87 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_add_kernel(float* x, con
         o[i] = from_f<TO>((xr[i] - mean2) * rstd2 * load_as_f(w2, w2_dtype, i) + load_as_f(b2, b2_dtype, i));
 }
 
+// Rows of up to 4096 entries, a multiple of 4, 16-byte aligned: a thread keeps its entries of y and x in registers (NV runs of four),
+// so that every row is read once and written once.
+__device__ __forceinline__ float4 ln_load4(const float* p, size_t i4) { return reinterpret_cast<const float4*>(p)[i4]; }
+__device__ __forceinline__ float4 ln_load4(const bf16* p, size_t i4) {
+    const uint2 r = reinterpret_cast<const uint2*>(p)[i4];
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ float4 ln_load4_as_f(const void* p, int dtype, size_t i4) {
+    return dtype == PE_F32 ? ln_load4((const float*)p, i4) : ln_load4((const bf16*)p, i4);
+}
+__device__ __forceinline__ void ln_store4(float* p, size_t i4, float4 v) { reinterpret_cast<float4*>(p)[i4] = v; }
+__device__ __forceinline__ void ln_store4(bf16* p, size_t i4, float4 v) {
+    uint2 r;
+    *reinterpret_cast<__nv_bfloat162*>(&r.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(&r.y) = __floats2bfloat162_rn(v.z, v.w);
+    reinterpret_cast<uint2*>(p)[i4] = r;
+}
+
+template <typename TY, typename TO, int NV>
+__global__ void __launch_bounds__(LN_THREADS) layernorm_add_vec_kernel(float* x, const TY* y, const void* w, int w_dtype, const void* b, int b_dtype,
+                                                                       float eps, int H, const void* w2, int w2_dtype, const void* b2, int b2_dtype,
+                                                                       float eps2, TO* out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int n4 = H / 4;
+    const size_t row4 = (size_t)blockIdx.x * n4;
+    float4 yv[NV], xv[NV];
+    float s = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int i = threadIdx.x + LN_THREADS * v;
+        if (i < n4) {
+            yv[v] = ln_load4(y, row4 + i);
+            xv[v] = ln_load4(x, row4 + i);
+            s += (yv[v].x + yv[v].y) + (yv[v].z + yv[v].w);
+        }
+    }
+    const float mean = block_sum(s, scratch) / (float)H;
+    float q = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v)
+        if (threadIdx.x + LN_THREADS * v < n4) {
+            const float a = yv[v].x - mean, c = yv[v].y - mean, d = yv[v].z - mean, e = yv[v].w - mean;
+            q += (a * a + c * c) + (d * d + e * e);
+        }
+    const float rstd = 1.0f / sqrtf(block_sum(q, scratch) / (float)H + eps);
+    float s2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int i = threadIdx.x + LN_THREADS * v;
+        if (i < n4) {
+            const float4 wv = ln_load4_as_f(w, w_dtype, i), bv = ln_load4_as_f(b, b_dtype, i);
+            xv[v].x += fmaf((yv[v].x - mean) * rstd, wv.x, bv.x); xv[v].y += fmaf((yv[v].y - mean) * rstd, wv.y, bv.y);
+            xv[v].z += fmaf((yv[v].z - mean) * rstd, wv.z, bv.z); xv[v].w += fmaf((yv[v].w - mean) * rstd, wv.w, bv.w);
+            ln_store4(x, row4 + i, xv[v]);
+            s2 += (xv[v].x + xv[v].y) + (xv[v].z + xv[v].w);
+        }
+    }
+    if (!out) return;
+    const float mean2 = block_sum(s2, scratch) / (float)H;
+    float q2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v)
+        if (threadIdx.x + LN_THREADS * v < n4) {
+            const float a = xv[v].x - mean2, c = xv[v].y - mean2, d = xv[v].z - mean2, e = xv[v].w - mean2;
+            q2 += (a * a + c * c) + (d * d + e * e);
+        }
+    const float rstd2 = 1.0f / sqrtf(block_sum(q2, scratch) / (float)H + eps2);
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int i = threadIdx.x + LN_THREADS * v;
+        if (i < n4) {
+            const float4 wv = ln_load4_as_f(w2, w2_dtype, i), bv = ln_load4_as_f(b2, b2_dtype, i);
+            ln_store4(out, row4 + i, make_float4(fmaf((xv[v].x - mean2) * rstd2, wv.x, bv.x), fmaf((xv[v].y - mean2) * rstd2, wv.y, bv.y),
+                                                 fmaf((xv[v].z - mean2) * rstd2, wv.z, bv.z), fmaf((xv[v].w - mean2) * rstd2, wv.w, bv.w)));
+        }
+    }
+}
+
 extern "C" int pe_layernorm_add(float* x, const void* y, int y_dtype, const void* w, int w_dtype, const void* b, int b_dtype, float eps,
                                 int T, int H, const void* w2, int w2_dtype, const void* b2, int b2_dtype, float eps2, void* out,
                                 int out_dtype, void* stream) {
@@ -364,6 +445,19 @@ extern "C" int pe_layernorm_add(float* x, const void* y, int y_dtype, const void
                                      w2_dtype, b2, b2_dtype, eps2, (TO*)out))
     const bool obf = out && out_dtype == PE_BF16;
     if (out && out_dtype != PE_BF16 && out_dtype != PE_F32) return PE_ERR_UNSUPPORTED;
+    const uintptr_t all = (uintptr_t)x | (uintptr_t)y | (uintptr_t)w | (uintptr_t)b | (uintptr_t)w2 | (uintptr_t)b2 | (uintptr_t)out;
+    if (H % 4 == 0 && H <= 4 * 4 * LN_THREADS && !(all & 15) && (y_dtype == PE_F32 || y_dtype == PE_BF16)) {
+        const int nv = (H / 4 + LN_THREADS - 1) / LN_THREADS;
+#define LNV(TY, TO, NV) PE_TRY(pe_launch(layernorm_add_vec_kernel<TY, TO, NV>, T, LN_THREADS, 0, s, x, (const TY*)y, w, w_dtype, b, b_dtype, eps, H, \
+                                         w2, w2_dtype, b2, b2_dtype, eps2, (TO*)out))
+#define LNV_N(TY, TO) do { if (nv <= 1) LNV(TY, TO, 1); else if (nv == 2) LNV(TY, TO, 2); else LNV(TY, TO, 4); } while (0)
+        if (y_dtype == PE_F32) { if (obf) LNV_N(float, bf16); else LNV_N(float, float); }
+        else { if (obf) LNV_N(bf16, bf16); else LNV_N(bf16, float); }
+#undef LNV_N
+#undef LNV
+        PE_LAUNCH_CHECK();
+        return 0;
+    }
     if (y_dtype == PE_F32) { if (obf) LNA(float, bf16); else LNA(float, float); }
     else if (y_dtype == PE_BF16) { if (obf) LNA(bf16, bf16); else LNA(bf16, float); }
     else return PE_ERR_UNSUPPORTED;

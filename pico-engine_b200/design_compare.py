@@ -3,11 +3,14 @@ with mixed heads or a minGRU recurrence, a dense relu^2 feed-forward, both halve
 (linear attention with fixed or learned decay, windowed softmax attention with an output gate beside it, gated dense
 feed-forwards and mixtures of experts) or the Pupidra decoder (post-norm layers with layer scale; windowed attention with a
 distance bias and kept first keys, also on another layer's keys and values; latent attention; a state-space mixer; ungated
-mixtures; a bigram embedding) and the dense Qwen2 decoder, this library's closest other model.  Random weights; prefill and decode throughput of a few layers, and
+mixtures; a bigram embedding) or the Tenusun decoder (a layer norm before and after each sublayer; latent attention with a query
+row behind a sliding window; grouped attention with one added to the softmax denominator, stretched rotation of halves, blended values and an
+output gate; a clamped gated feed-forward; mixtures chosen by sigmoid scores among groups of experts; its kernels also beside Pupidra's like
+kernels) and the dense Qwen2 decoder, this library's closest other model.  Random weights; prefill and decode throughput of a few layers, and
 the kernels of the new design each beside the Qwen2 kernel that does the like job, as fractions of the measured
 copy bandwidth or matrix throughput.
 
-    python -m pico_engine.design_compare [--design mebalorn|kevelorn|pupidra] [--sizes s,m,l] [--tokens 2048] [--batch 8] [--context 2048] [--output FILE]
+    python -m pico_engine.design_compare [--design mebalorn|kevelorn|pupidra|tenusun] [--sizes s,m,l] [--tokens 2048] [--batch 8] [--context 2048] [--output FILE]
 """
 from __future__ import annotations
 
@@ -45,7 +48,14 @@ def pupidra_config(size: str, layers: int | None = None) -> dict:
     return pupidra_shape(W, H, G, D, F, layers or max(L, 4), VOCAB)          # four layers: every kind of mixer once
 
 
-DESIGNS = {"mebalorn": mebalorn_config, "kevelorn": kevelorn_config, "pupidra": pupidra_config}
+def tenusun_config(size: str, layers: int | None = None) -> dict:
+    from .config.shapes import tenusun_shape
+    W, H, G, D, F, L = SIZES[size]
+    return tenusun_shape(W, H, G, D, F, layers or max(L, 4), VOCAB)          # four layers: both kinds of layer twice (the second attention blends values)
+
+
+DESIGNS = {"mebalorn": mebalorn_config, "kevelorn": kevelorn_config, "pupidra": pupidra_config, "tenusun": tenusun_config}
+FOUR_LAYERS = ("pupidra", "tenusun")
 
 
 def qwen2_config(size: str, layers: int | None = None) -> dict:
@@ -281,6 +291,81 @@ def pupidra_kernel_times(eng, size: str, tokens: int, batch: int, context: int, 
     B.close_sequences(eng, slots)
 
 
+def tenusun_kernel_times(eng, size: str, tokens: int, batch: int, context: int, entry) -> None:
+    """The kernels of the Tenusun parts at the sizes of this shape's layers (layers 0 and 2 latent attention + dense feed-forward,
+    layers 1 and 3 attention + mixture; layer 3 blends its values with layer 1's)."""
+    W, H, G, D, F, L = SIZES[size]
+    bf = torch.bfloat16
+    layers = eng.model.layers
+    e_lat, e_att, e_mix = 0, 1, 3
+    lat, att, att2 = layers[e_lat].mixer, layers[e_att].mixer, layers[e_mix].mixer
+    dense, moe = layers[e_lat].feed_forward, layers[e_att].feed_forward
+    sa, sl = att.spec, lat.spec
+    Dv, rank, R = sa.v_head_dim, sl.kv_rank, sl.rot_dim
+    q_w, dkv_w, _ = lat._widths()
+
+    def attention_calls(ctx, T, label, seen_all, seen_window, nbytes_plain=None, nbytes_latent=None):
+        kv = ctx.kv(e_att)
+        qkv = torch.randn(T, att.w_in.shape[0], device="cuda").to(bf)
+        how = dict(flops=2.0 * H * (D + Dv) * seen_all) if nbytes_plain is None else dict(nbytes=nbytes_plain)
+        entry(f"{label} attention (one added to the denominator)", device_us(lambda: kernels.attention_headmix(
+            qkv, qkv.shape[1], H, G, D, Dv, kv.k, kv.v, kv.table, kv.stride, ctx.tok_pos, ctx.tok_row, None, sa.scale, att.sink, None, ctx)), **how)
+        kl = ctx.kv(e_lat)
+        ql = torch.randn(T, H * (rank + R), device="cuda").to(bf)
+        how = dict(flops=2.0 * H * (2 * rank + R) * seen_window) if nbytes_latent is None else dict(nbytes=nbytes_latent)
+        entry(f"{label} attention over latent rows (window)", device_us(lambda: kernels.attention_headmix(
+            ql, ql.shape[1], H, 1, rank + R, rank, kl.k, None, kl.table, kl.stride, ctx.tok_pos, ctx.tok_row, sl.window, sl.scale, None, None, ctx,
+            values_in_keys=True)), **how)
+
+    slot, ctx = _prompt_context(eng, tokens)
+    window = sl.window or tokens
+    attention_calls(ctx, tokens, "prefill", tokens * (tokens + 1) / 2, sum(min(p + 1, window) for p in range(tokens)))
+    kv = ctx.kv(e_mix)
+    qkv = torch.randn(tokens, att2.w_in.shape[0], device="cuda").to(bf)
+    other = torch.randn(tokens, att.w_in.shape[0], device="cuda").to(bf)[:, (H + G) * D:(H + G) * D + G * Dv]
+    entry("prefill rotation of halves + blended values + cache write", device_us(lambda: kernels.rotary_half_store(
+        qkv, H, G, D, Dv, att2.freq, sa.position.dims, att2.magnitude, False, sa.norm_eps, ctx.tok_pos, ctx.tok_row, kv.k, kv.v, kv.table, kv.stride,
+        other, att2.blend_weight)), nbytes=tokens * ((H + G) * D * 2 * 2 + G * D * 2 + G * Dv * 2 * 4))
+    a = torch.randn(tokens, H * Dv, device="cuda").to(bf)
+    entry("prefill heads x sigmoid(gate)", device_us(lambda: kernels.gated_norm(a, 0, None, sa.norm_eps, qkv, (H + G) * D + G * Dv, "sigmoid", bf)),
+          nbytes=tokens * H * Dv * 2 * 3)
+    kl = ctx.kv(e_lat)
+    proj = torch.randn(tokens, lat.w_in.shape[0], device="cuda").to(bf)
+    entry("prefill norm of the query row", device_us(lambda: kernels.rmsnorm_cols(proj, 0, sl.q_rank, lat.dq_norm, sl.norm_eps)), nbytes=tokens * sl.q_rank * 2 * 2)
+    q_rows = torch.randn(tokens, H * (sl.head_dim + R), device="cuda").to(bf)
+    q_abs = torch.randn(H, tokens, rank, device="cuda").to(bf)
+    entry("prefill latent norm + rotation + cache write + query rows", device_us(lambda: kernels.latent_prepare(
+        proj, H, sl.head_dim, R, rank, q_w, lat.dkv_norm, sl.norm_eps, lat.freq, sl.position.dims, q_abs, ctx.tok_pos, ctx.tok_row, kl.k,
+        kl.table, kl.stride, halves=True, q_rows=q_rows)), nbytes=tokens * 2 * (H * (rank + R) * 2 + H * R + 2 * (rank + R)))
+    o = torch.randn(H, tokens, sl.v_head_dim, device="cuda").to(bf)
+    entry("prefill heads out of head-major rows", device_us(lambda: kernels.head_gate(o, None, 0)), nbytes=tokens * H * sl.v_head_dim * 2 * 2)
+    x = torch.randn(tokens, W, device="cuda")
+    y = torch.randn(tokens, W, device="cuda")
+    n1, n2 = layers[e_lat].mixer_out_norm, layers[e_lat].feed_forward_norm
+    entry("prefill output norm into the stream + next norm", device_us(lambda: kernels.layernorm_add(
+        x, y, n1.weight, n1.bias, n1.eps, (n2.weight, n2.bias, n2.eps), bf)), nbytes=tokens * W * (4 * 3 + 2))
+    gu = torch.randn(tokens, 2 * F, device="cuda").to(bf)
+    entry("prefill clamped gate x (up + 1)", device_us(lambda: kernels.gated_act(gu, "clamped_sigmoid", limit=dense.spec.limit, alpha=dense.spec.alpha)),
+          nbytes=tokens * F * 2 * 3)
+    E, top = moe.spec.n_experts, moe.spec.top_k
+    h = torch.randn(tokens, W, device="cuda").to(bf)
+    n3 = layers[e_att].feed_forward_norm
+    entry("prefill layer norm + router + sigmoid scores + choice among groups", device_us(lambda: kernels.moe_route_stream_grouped(
+        x, n3.weight, n3.bias, n3.eps, moe.w_router, E, top, moe.correction, moe.spec.n_groups, moe.spec.keep_groups, moe.spec.group_best,
+        moe.spec.route_scale)), nbytes=tokens * (W * 4 + E * 4))
+    I = moe.w_down.shape[1]
+    gum = torch.randn(tokens, 2 * I, device="cuda").to(bf)
+    wts = moe.routing(h)
+    entry("prefill silu(gate) x up x expert weight", device_us(lambda: kernels.gated_act(gum, "silu", wts, moe.spec.intermediate)), nbytes=tokens * I * 2 * 3)
+    ids = torch.randint(0, VOCAB, (tokens,), device="cuda", dtype=torch.int32)
+    entry("prefill token rows x scale", device_us(lambda: kernels.embed(eng.model.embedding, ids, scale=eng.model.plan.embedding_scale)), nbytes=tokens * W * (2 + 4))
+    eng.cache.close(slot)
+    slots, ctx = _decode_context(eng, batch, context)
+    attention_calls(ctx, batch, "decode", 0, 0, nbytes_plain=batch * context * G * (D + Dv) * 2,
+                    nbytes_latent=batch * min(context, window) * (rank + R) * 2)
+    B.close_sequences(eng, slots)
+
+
 def kernel_times(size: str, tokens: int, batch: int, context: int, peaks: dict, design: str = "mebalorn") -> Dict[str, dict]:
     """Every kernel of the new design beside the like kernel of the Qwen2 decoder: microseconds, the bytes or
     multiply-adds it must move or do, and that as a fraction of the measured peak."""
@@ -300,11 +385,19 @@ def kernel_times(size: str, tokens: int, batch: int, context: int, peaks: dict, 
     entry.out = out
     # (the kernels of the Kevelorn parts are timed in a model of three layers, which has every kind of part once)
     first = kevelorn_config(size, 3) if design == "kevelorn" else DESIGNS[design](size)
-    for design, cfg in ((design, first), ("qwen2", qwen2_config(size))):
-        if design == "pupidra":
+    runs = [(design, first), ("qwen2", qwen2_config(size))]
+    if design == "tenusun":                                  # its kernels also beside the like kernels of Pupidra
+        runs.insert(1, ("pupidra beside", pupidra_config(size)))
+    for design, cfg in runs:
+        if design in ("pupidra", "pupidra beside", "tenusun"):
             eng = Engine.from_config(config_from_dict(cfg), seed=1, draw_on="cuda", dtype="bfloat16")
             eng.ensure_cache(max(tokens, batch * context) + 64 * batch, max(tokens, context), max_seqs=batch + 1)
-            pupidra_kernel_times(eng, size, tokens, batch, context, entry)
+            if design == "tenusun":
+                tenusun_kernel_times(eng, size, tokens, batch, context, entry)
+            elif design == "pupidra":
+                pupidra_kernel_times(eng, size, tokens, batch, context, entry)
+            else:
+                pupidra_kernel_times(eng, size, tokens, batch, context, _prefixed(entry, out))
             kernels.check_status(eng.device)
             del eng
             torch.cuda.empty_cache()
@@ -376,12 +469,33 @@ def kernel_times(size: str, tokens: int, batch: int, context: int, peaks: dict, 
     return out
 
 
+class _prefixed:
+    """``entry`` under names that begin with "pupidra ": the like kernels of another design in the same record."""
+
+    def __init__(self, entry, out):
+        self.entry, self.out = entry, _PrefixedDict(out)
+
+    def __call__(self, name, us, nbytes=None, flops=None):
+        self.entry("pupidra " + name, us, nbytes, flops)
+
+
+class _PrefixedDict:
+    def __init__(self, out):
+        self._out = out
+
+    def __getitem__(self, name):
+        return self._out["pupidra " + name]
+
+
 def throughput(size: str, tokens: int, batch: int, context: int, steps: int = 64, design: str = "mebalorn") -> Dict[str, dict]:
-    """Prefill of one prompt and decode of ``batch`` sequences through the engines' own steps, both designs."""
+    """Prefill of one prompt and decode of ``batch`` sequences through the engines' own steps, both designs (for Tenusun also Pupidra)."""
     from .engine.engine import Engine
     out = {}
-    n_layers = max(SIZES[size][5], 4) if design == "pupidra" else None      # the same number of layers on both sides
-    for design, cfg in ((design, DESIGNS[design](size)), ("qwen2", qwen2_config(size, n_layers))):
+    n_layers = max(SIZES[size][5], 4) if design in FOUR_LAYERS else None    # the same number of layers on both sides
+    runs = [(design, DESIGNS[design](size)), ("qwen2", qwen2_config(size, n_layers))]
+    if design == "tenusun":
+        runs.insert(1, ("pupidra", pupidra_config(size)))
+    for design, cfg in runs:
         eng = Engine.from_config(config_from_dict(cfg), seed=1, draw_on="cuda", dtype="bfloat16")
         pre = B.prefill_device(eng, tokens)
         dec = B.decode_device(eng, batch, context, steps, 4)
@@ -396,7 +510,7 @@ def throughput(size: str, tokens: int, batch: int, context: int, steps: int = 64
 
 def compare(sizes, tokens: int, batch: int, context: int, peaks: dict, design: str = "mebalorn") -> dict:
     record = {"tokens": tokens, "batch": batch, "context": context,
-              "layers": {s: max(SIZES[s][5], 4) if design == "pupidra" else SIZES[s][5] for s in sizes},
+              "layers": {s: max(SIZES[s][5], 4) if design in FOUR_LAYERS else SIZES[s][5] for s in sizes},
               "widths": {s: dict(zip(("width", "heads", "kv_heads", "head_dim", "ff"), SIZES[s][:5])) for s in sizes}, "sizes": {}}
     for s in sizes:
         record["sizes"][s] = {"throughput": throughput(s, tokens, batch, context, design=design),

@@ -289,10 +289,11 @@ def attention_decode(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: i
                      k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, table_stride: int,
                      tok_pos: torch.Tensor, tok_row: torch.Tensor, window: Optional[int], scale: float,
                      max_context: int, out: Optional[torch.Tensor] = None, early_pages: bool = True, keep_first: int = 0,
-                     slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of T single tokens (bfloat16) over the cache; ``max_context`` bounds every
     token's position + 1 and fixes the launch shape.  ``keep_first``: with a window, a sequence's first so many keys stay
-    visible.  ``slopes`` float32 [H]: slope_h * (i - j) is taken off the score of query i and key j.  With ``early_pages`` the kernel copies cache pages
+    visible.  ``slopes`` float32 [H]: slope_h * (i - j) is taken off the score of query i and key j.  ``sinks`` float32 [H]: one more place of
+    score sinks[h] joins every softmax denominator of head h and carries no value.  With ``early_pages`` the kernel copies cache pages
     while the two kernels before it on the stream may still run: they must have written keys and values
     at each token's own position only (the library's own parts do).  A part that rewrites other cache
     rows shortly before attending passes False: the kernel then starts when everything before it has ended."""
@@ -311,7 +312,7 @@ def attention_decode(q: torch.Tensor, q_stride: int, n_heads: int, n_kv_heads: i
                                   block_table.data_ptr(), table_stride, tok_pos.data_ptr(), tok_row.data_ptr(), T,
                                   n_heads, n_kv_heads, head_dim, window or 0, float(scale), int(max_context),
                                   1 if early_pages else 0, status_ptr(q.device), stream_ptr(), int(keep_first) if window else 0,
-                                  _ptr(slopes)), "attention_decode")
+                                  _ptr(slopes), _ptr(sinks)), "attention_decode")
     return out
 
 
@@ -373,17 +374,19 @@ def attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, n_heads: int, n_kv
                               k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, table_stride: int,
                               tiles: torch.Tensor, n_tokens: int, window: Optional[int], scale: float,
                               out: Optional[torch.Tensor] = None, keep_first: int = 0,
-                              slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
+                              slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The same on the tcgen05 tensor cores, for head sizes 64 and 128 and runs ``tiles`` of at most
     128 tokens.  ``q`` is a view of ``n_tokens`` rows, ``q_stride`` elements apart.  ``keep_first``: with a window, the first so
     many keys of a sequence stay visible.  ``slopes`` float32 [heads]: slope_h * (i - j) is taken off the score of query i and
-    key j."""
+    key j.  ``sinks`` float32 [heads]: one more place of score sinks[h] joins every softmax denominator of head h and carries no value."""
     from .library import for_head_dim
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32, (n_heads,))
     out = _prefill_args(q, n_heads, n_kv_heads, head_dim, k_pool, v_pool, block_table, tiles, n_tokens, out)
     check(for_head_dim(head_dim).pe_attention_prefill_tcgen05(
         q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0], block_table.data_ptr(),
         table_stride, tiles.data_ptr(), tiles.shape[0], n_tokens, n_heads, n_kv_heads, head_dim, window or 0,
-        float(scale), keep_first if window else 0, _ptr(slopes), status_ptr(q.device), stream_ptr()), "attention_prefill_tcgen05")
+        float(scale), keep_first if window else 0, _ptr(slopes), status_ptr(q.device), stream_ptr(), _ptr(sinks)), "attention_prefill_tcgen05")
     return out
 
 
@@ -862,23 +865,24 @@ def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, h
         _need(sink, "sink", None, (n_heads,))
     if mix is not None:
         _need(mix, "mix", None, (n_heads, n_heads))
-    if (q.dtype == torch.bfloat16 and not ctx.one_token_each and sink is None and mix is None and not values_in_keys
+    sink_f32 = sink is None or sink.dtype == torch.float32
+    if (q.dtype == torch.bfloat16 and not ctx.one_token_each and sink_f32 and mix is None and not values_in_keys
             and head_dim == v_head_dim and attention_prefill_tcgen05_takes(head_dim, scale) and q_stride % 8 == 0
             and HEADMIX_TENSOR_CORES == "1"):
         # one weight a (query, key) and equal sizes of 64 or 128: the tcgen05 kernel of the plain attention, which takes the
-        # distance's share of the score and the kept first keys
+        # distance's share of the score, the kept first keys and a sink logit a head
         tiles = ctx.scratch.get("prefill_tiles_128")
         if tiles is None:
             tiles = ctx.scratch["prefill_tiles_128"] = prefill_tiles(ctx.lens, ctx.starts, q.device, PREFILL_TILE_TCGEN05)
         return attention_prefill_tcgen05(q, q_stride, n_heads, n_kv, head_dim, k_pool, v_pool, block_table, table_stride, tiles, T,
-                                         window, scale, keep_first=keep_first, slopes=slopes)
-    if (q.dtype == torch.bfloat16 and ctx.one_token_each and sink is None and mix is None and not values_in_keys
+                                         window, scale, keep_first=keep_first, slopes=slopes, sinks=sink)
+    if (q.dtype == torch.bfloat16 and ctx.one_token_each and sink_f32 and mix is None and not values_in_keys
             and head_dim == v_head_dim and attention_prefill_tcgen05_takes(head_dim, scale) and q_stride % 8 == 0
             and HEADMIX_TENSOR_CORES == "1"):
         # single tokens at the same sizes: the decode kernel of the plain attention, which knows both as well (the kernels before
         # it in the stream write no cache row but each token's own)
         return attention_decode(q, q_stride, n_heads, n_kv, head_dim, k_pool, v_pool, block_table, table_stride, tok_pos, tok_row,
-                                window, scale, ctx.max_context, keep_first=keep_first, slopes=slopes)
+                                window, scale, ctx.max_context, keep_first=keep_first, slopes=slopes, sinks=sink)
     lib = mixers()
     tiles, n_runs = None, 0
     if not ctx.one_token_each:
@@ -899,7 +903,9 @@ def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, h
             # 51 us at 2 / 4 / 8 / 16 / 32 ranges, 16 heads of 128 on 4 key/value heads 82 / 55 / 70 / 97 / 202 us: more ranges
             # mean more partial outputs to write and merge.  A prompt has blocks enough and is not cut (2,048 tokens: 183 us
             # uncut, 209 us in two ranges).
-            splits = max(1, min((224 + blocks - 1) // blocks, (ctx.max_context + 63) // 64, 64))
+            # (a window leaves a token the pages of its last `window` keys and of the kept first ones: no more ranges than those)
+            span = ctx.max_context if not window else min(ctx.max_context, window + PAGE - 1 + (keep_first + PAGE - 1) // PAGE * PAGE)
+            splits = max(1, min((224 + blocks - 1) // blocks, (span + 63) // 64, 64))
             ws = scratch("attention_headmix", 4 * lib.pe_attention_flashmix_scratch_floats(T, splits, n_heads, n_kv, v_head_dim, 1 if tiles is None else 0), q.device)
             check(lib.pe_attention_flashmix(q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
                                             block_table.data_ptr(), table_stride, tok_pos.data_ptr(), tok_row.data_ptr(), _ptr(tiles),
@@ -1361,4 +1367,25 @@ def moe_route_grouped(logits: torch.Tensor, n_experts: int, top_k: int, correcti
     check(gated().pe_moe_route_grouped(logits.data_ptr(), logits.shape[1], n_experts, top_k, _ptr(correction),
                                        0 if correction is None else _code(correction, "correction"), n_groups, keep, group_best,
                                        float(factor), out.data_ptr(), _ptr(ids), T, stream_ptr()), "moe_route_grouped")
+    return out
+
+
+def moe_route_stream_grouped(x: torch.Tensor, norm_weight: torch.Tensor, norm_bias: torch.Tensor, eps: float, router: torch.Tensor,
+                             n_experts: int, top_k: int, correction: Optional[torch.Tensor], n_groups: int, keep: int, group_best: int = 2,
+                             factor: float = 1.0, ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``moe_route_grouped`` of the logits router . layernorm(x): x float32 [T, K] is the residual stream, ``norm_weight`` and
+    ``norm_bias`` [K] the layer norm in front of the router, ``router`` float32 [E, K]; norm, logits and choice are one kernel, all
+    in float32 (up to 256 experts)."""
+    T, K = x.shape
+    _need(x, "x", torch.float32); _need(router, "router", torch.float32, (n_experts, K))
+    _need(norm_weight, "norm_weight", None, (K,)); _need(norm_bias, "norm_bias", None, (K,))
+    if correction is not None:
+        _need(correction, "correction", None, (n_experts,))
+    if ids is not None:
+        _need(ids, "ids", torch.int32, (T, top_k))
+    out = torch.empty(T, n_experts, dtype=torch.float32, device=x.device)
+    check(gated().pe_moe_route_stream_grouped(x.data_ptr(), norm_weight.data_ptr(), _code(norm_weight, "norm_weight"), norm_bias.data_ptr(),
+                                              _code(norm_bias, "norm_bias"), float(eps), router.data_ptr(), K, n_experts, top_k,
+                                              _ptr(correction), 0 if correction is None else _code(correction, "correction"), n_groups, keep,
+                                              group_best, float(factor), out.data_ptr(), _ptr(ids), T, stream_ptr()), "moe_route_stream_grouped")
     return out

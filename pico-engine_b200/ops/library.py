@@ -78,6 +78,7 @@ _GATED_SIGNATURES = {
     "pe_weighted_act": [P, P, I, I, I, I, P, I, I, P],
     "pe_moe_route": [P, I, I, I, I, P, P, I, I, F, P],
     "pe_moe_route_grouped": [P, I, I, I, P, I, I, I, I, F, P, P, I, P],
+    "pe_moe_route_stream_grouped": [P, P, I, P, I, F, P, I, I, I, P, I, I, I, I, F, P, P, I, P],
     "pe_rotary_half_store": [P, I, I, I, I, I, I, I, P, I, F, I, F, P, P, P, P, P, I, I, P, I, P, I, P],
     "pe_moe_route_stream": [P, P, I, F, P, I, I, I, I, P, P, I, I, F, P],
 }
@@ -102,10 +103,10 @@ _EXTRA_SIGNATURES = {
 }
 
 _HEAD_DIM_SIGNATURES = {
-    "pe_attention_decode": [P, I, P, P, P, P, I, P, P, I, I, I, I, I, F, I, I, P, P, I, P],
+    "pe_attention_decode": [P, I, P, P, P, P, I, P, P, I, I, I, I, I, F, I, I, P, P, I, P, P],
     "pe_attention_decode_splits": [I, I, I, I, P],
     "pe_attention_prefill": [P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, F, P],
-    "pe_attention_prefill_tcgen05": [P, I, P, P, P, LL, P, I, P, I, I, I, I, I, I, F, I, P, P, P],
+    "pe_attention_prefill_tcgen05": [P, I, P, P, P, LL, P, I, P, I, I, I, I, I, I, F, I, P, P, P, P],
 }
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}

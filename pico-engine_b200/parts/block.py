@@ -220,4 +220,6 @@ def sandwich(layer: Layer, x, ctx, entry, cache_entry, owns_cache) -> None:
             raise ConfigError("the sandwich arrangement takes a norm on every sublayer's output")
         h = ctx.normed(x, norm)
         extra = {"out_dtype": x.dtype} if getattr(part, "takes_out_dtype", False) else {}
+        if part is layer.feed_forward and getattr(part, "routes_from_stream", False):
+            extra["x_norm"] = (x, norm)                      # a router may read the float32 stream through the norm itself
         ctx.defer_normed_add(x, part.apply(h, ctx, *where, **extra), out_norm)

@@ -114,9 +114,17 @@ class Mixture(FeedForward):
                 weights = kernels.moe_route_stream(x, None, 0.0, self.w_router, s.n_experts, s.top_k, self._extra(), **how)
                 gate_up = linear(norm.forward(x, ctx.dtype) if h is None else h, self.w_gate_up, out_dtype=ctx.dtype)
         else:
+            from .norm import LayerNorm
             if h is None:
                 h = x_norm[1].forward(x_norm[0], ctx.dtype)
-            weights = self.routing(h)
+            if (x_norm is not None and s.scores == "sigmoid" and type(x_norm[1]) is LayerNorm
+                    and s.n_experts <= kernels.MOE_ROUTE_STREAM_MAX_EXPERTS):
+                # the router reads the float32 stream through its layer norm inside the routing kernel
+                x, norm = x_norm
+                weights = kernels.moe_route_stream_grouped(x, norm.weight, norm.bias, norm.eps, self.w_router, s.n_experts, s.top_k,
+                                                           self.correction, s.n_groups, s.keep_groups, s.group_best, s.route_scale)
+            else:
+                weights = self.routing(h)
             gate_up = linear(h, self.w_gate_up, out_dtype=ctx.dtype)
         if not s.gated:
             return kernels.weighted_act(gate_up, s.activation, weights, s.intermediate)

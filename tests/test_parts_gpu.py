@@ -120,8 +120,8 @@ def test_unknown_part_and_arrangement_are_refused():
     from pico_engine.parts import MIXERS, Layer, build_part
     with pytest.raises(ConfigError, match="no mixer is registered"):
         build_part(MIXERS, "mixer", PartSpec(), torch.float32, "cuda")
-    spec = replace(config_from_dict(TINY_B).plan().layers[0], arrangement="sandwich")
-    with pytest.raises(ConfigError, match="sandwich"):
+    spec = replace(config_from_dict(TINY_B).plan().layers[0], arrangement="braided")
+    with pytest.raises(ConfigError, match="braided"):
         Layer(spec, torch.float32, "cuda")
 
 

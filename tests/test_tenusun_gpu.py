@@ -254,11 +254,12 @@ def test_attention_with_one_added_to_the_denominator(dtype, H, G, D, Dv):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_very_low_scores_leave_the_added_one_alone(dtype):
+@pytest.mark.parametrize("D,Dv", [(32, 16), (64, 64), (128, 128)])
+def test_very_low_scores_leave_the_added_one_alone(dtype, D, Dv):
     """Every score far below zero: the weights vanish beside the added one and the output is zero, not a mean of the values;
-    the first token of a sequence, which sees only itself, included."""
+    the first token of a sequence, which sees only itself, included (at the head sizes of every attention kernel)."""
     dt = DTYPES[dtype]
-    n, H, G, D, Dv = 70, 2, 1, 32, 16
+    n, H, G = 70, 2, 1
     q, k, v = torch.zeros(n, H, D), torch.zeros(n, G, D), torch.ones(n, G, Dv) * 5
     q[:, :, 0], k[:, :, 0] = 8.0, -8.0                                  # every score is -64
     kp, table = paged(k, dt)
@@ -269,6 +270,24 @@ def test_very_low_scores_leave_the_added_one_alone(dtype):
     q[:, :, 0] = -8.0                                                   # every score is +64: the added one vanishes
     got = run_attention(q, kp, vp, table, dt, [(0, n)], None, 1.0, Dv, sink=0.0)
     assert (got - 5.0).abs().max() < 1e-3
+
+
+@pytest.mark.parametrize("H,G,D", [(4, 2, 64), (2, 1, 128), (3, 1, 64), (16, 2, 128)])
+def test_long_prompts_in_bfloat16_at_head_sizes_of_the_tensor_memory_kernel(H, G, D):
+    """Prompts of 900 tokens with the added one at the sizes the tcgen05 prompt kernel and the cluster kernel for single tokens take:
+    whole, in portions that begin and end off the borders of pages and of the kernel's runs of tokens, and with the last 330 tokens
+    one by one (the ranges of keys that several blocks share are merged before the added one joins)."""
+    dt, n = torch.bfloat16, 900
+    g = torch.Generator().manual_seed(H * 100 + D)
+    q, k, v = ((torch.randn(n, h, D, generator=g)).to(dt).float() for h in (H, G, G))
+    scale = 0.3 * D ** -0.5
+    want = plain_attention(q.double(), k.double(), v.double(), scale, None, True)
+    assert (want - plain_attention(q.double(), k.double(), v.double(), scale, None, False)).abs().max() > 0.05
+    kp, table = paged(k, dt)
+    vp, _ = paged(v, dt)
+    for spans in ([(0, n)], [(0, 130), (130, 133), (133, 517), (517, n)], [(0, 570)] + [(p, p + 1) for p in range(570, n)]):
+        got = run_attention(q, kp, vp, table, dt, spans, None, scale, D, sink=0.0)
+        assert (got.double() - want).abs().max() < 2e-2 * max(1.0, float(want.abs().max())), spans[:2]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -405,7 +424,7 @@ def test_latent_rows_in_the_layout_of_halves(dtype, H, D, R, rank, q_rank):
 # ------------------------------------------------------------------ norms on a sublayer's output, the clamped activation, the choice of experts
 
 @pytest.mark.parametrize("ydtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("W", [50, 256, 1000])
+@pytest.mark.parametrize("W", [50, 256, 1000, 3584, 4100])
 def test_normed_output_into_the_stream_and_the_next_norm(ydtype, W):
     from pico_engine.ops import kernels
     g = torch.Generator().manual_seed(W)
@@ -464,3 +483,50 @@ def test_choice_of_experts_among_groups(E, top, groups):
         assert (got[t].double() - want).abs().max() < 1e-6, (t, got[t], want)
         assert ids[t].tolist() == [e for e, _ in chosen[t]]
     assert (got > 0).sum(1).tolist() == [top] * T
+
+
+@pytest.mark.parametrize("K,E,top,groups", [(50, 6, 2, (6, 3)), (80, 8, 3, (4, 2)), (256, 12, 2, (2, 1)), (1000, 64, 6, (8, 3)), (128, 2, 2, (1, 1))])
+def test_router_on_the_stream_through_its_layer_norm(K, E, top, groups):
+    """Layer norm, router product and the choice among groups in one kernel on float32 rows, against the plain functions."""
+    from pico_engine.ops import kernels
+    g = torch.Generator().manual_seed(K + E)
+    T, eps = 40, 1e-5
+    x = torch.randn(T, K, generator=g) * 3 + 0.5
+    nw, nb = (1 + 0.2 * torch.randn(K, generator=g)).to(torch.bfloat16), (0.2 * torch.randn(K, generator=g)).to(torch.bfloat16)
+    router, corr = torch.randn(E, K, generator=g) * 1.5 * K ** -0.5, torch.randn(E, generator=g) - 0.3
+    h = plain.layer_norm(x.double(), nw.double(), nb.double(), eps)
+    w = {"p.router": router.double(), "p.correction": corr.double()}
+    plain.ROUTER_GAPS = []
+    chosen = plain.route(h, {"router": {"experts": E, "top": top, "groups": {"count": groups[0], "keep": groups[1]}}}, w, "p.")
+    gaps, plain.ROUTER_GAPS = plain.ROUTER_GAPS[0], None
+    ids = torch.zeros(T, top, dtype=torch.int32).cuda()
+    got = kernels.moe_route_stream_grouped(x.cuda(), nw.cuda(), nb.cuda(), eps, router.cuda(), E, top, corr.cuda(), groups[0], groups[1], 2, 1.0, ids).cpu()
+    compared = 0
+    for t in range(T):
+        if gaps[t] < 1e-4:                                   # (a choice that float32 rounding can turn)
+            continue
+        compared += 1
+        want = torch.zeros(E, dtype=torch.float64)
+        for e, sc in chosen[t]:
+            want[e] = sc
+        assert (got[t].double() - want).abs().max() < 1e-5, (t, got[t], want)
+        assert ids[t].tolist() == [e for e, _ in chosen[t]]
+    assert compared > T // 2
+
+
+@pytest.mark.parametrize("ff,experts", [(24, 8), (32, 8), (20, 6), (64, 4)])
+def test_gated_activation_times_expert_weights_leaves_unused_experts_at_zero(ff, experts):
+    """silu(gate) * up * weight(token, expert) with the hidden units of all experts side by side; experts a token does not use give
+    exact zeros, also where they hold infinities (their columns are not read where the kernel can tell)."""
+    from pico_engine.ops import kernels
+    g = torch.Generator().manual_seed(ff)
+    T, I = 9, ff * experts
+    for dt in (torch.float32, torch.bfloat16):
+        gu = torch.randn(T, 2 * I, generator=g).to(dt)
+        wts = torch.rand(T, experts, generator=g)
+        wts[torch.rand(T, experts, generator=g) < 0.6] = 0.0
+        col = wts.repeat_interleave(ff, dim=1).double()
+        want = gu[:, :I].double() * plain.sigmoid(gu[:, :I].double()) * gu[:, I:].double() * col
+        got = kernels.gated_act(gu.cuda(), "silu", wts.cuda(), ff).double().cpu()
+        assert (got - want).abs().max() < (1e-5 if dt == torch.float32 else 2e-2)
+        assert bool((got[col == 0] == 0).all())
