@@ -35,6 +35,8 @@ struct FlashMixArgs {
                                                      // visible behind the window; a value row has v_ld entries of which the first Dv are read;
                                                      // v_in_k: the values are the front of the one key head's rows and are read from K's copy
     float* pm; float* pl; float* po;          // [T][splits][H], [T][splits][H], [T][splits][H][G][Dv]
+    bf16* direct; const float* sink;          // direct != null (one range, no mixing): a head's output is complete in the block that has its
+                                              // key/value head: it is normalised (with exp(sink) in the denominator) and written there
 };
 
 __device__ __forceinline__ void fx_ldsm_x2(uint32_t (&r)[2], const void* p) {
@@ -272,6 +274,23 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
         l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
         l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 2);
     }
+    if (a.direct) {
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            const int ci = head[rr] / per_kv - c_lo;              // the head's own value head among this block's
+            if (!live[rr] || ci < 0 || ci >= c_n) continue;
+            float den = l[rr];
+            if (a.sink) den += exp2f(fmaf(a.sink[head[rr]], 1.4426950408889634f, -m[rr]));      // (m in powers of two)
+            const float inv = den > 0.f ? 1.0f / den : 0.f;
+            bf16* dst = a.direct + ((size_t)tok[rr] * H + head[rr]) * Dv;
+#pragma unroll
+            for (int n = 0; n < NVM; ++n) {
+                if (n < nv && n / nvt == ci)
+                    *reinterpret_cast<__nv_bfloat162*>(dst + (n % nvt) * 8 + (lane & 3) * 2) = __floats2bfloat162_rn(o[n][rr * 2] * inv, o[n][rr * 2 + 1] * inv);
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
         if (!live[rr]) continue;
@@ -408,7 +427,8 @@ extern "C" int pe_attention_flashmix(const void* q, int q_stride, void* out, con
     float* pl = pm + (size_t)T * parts * H;
     float* po = pl + (size_t)T * parts * H;
     FlashMixArgs a = {(const bf16*)q, q_stride, (const bf16*)k_pool, (const bf16*)v_pool, table, table_stride, tok_pos, tok_row, tiles,
-                      H, G, D, Dv, window, scale, splits, cg, ngroups, slopes, keep_first, v_ld, 0, pm, pl, po};
+                      H, G, D, Dv, window, scale, splits, cg, ngroups, slopes, keep_first, v_ld, 0, pm, pl, po, nullptr, sink};
+    if (parts == 1 && !mix && !(((uintptr_t)out) & 3) && Dv % 2 == 0) a.direct = (bf16*)out;      // no partial results, no merge
     a.v_in_k = (v_pool == k_pool && G == 1 && v_ld == D) ? 1 : 0;                  // one copy of a page serves as keys and values
     const size_t smem = 2 * 2 * ((size_t)PE_PAGE * (D + FX_PAD) + (a.v_in_k ? 0 : (size_t)cg * PE_PAGE * (Dv + FX_PAD)));      // two stages of bfloat16
     const size_t merge_smem = sizeof(float) * (2 * (size_t)H * parts + 2 * (size_t)H + 1024);       // (room for the most threads)
@@ -421,6 +441,7 @@ extern "C" int pe_attention_flashmix(const void* q, int q_stride, void* out, con
     else if (dk <= 8) rc = nv <= 16 ? fx_launch<8, 16>(a, sub, grid, smem, s) : fx_launch<8, 32>(a, sub, grid, smem, s);
     else rc = nv <= 16 ? fx_launch<16, 16>(a, sub, grid, smem, s) : fx_launch<16, 32>(a, sub, grid, smem, s);
     if (rc) return rc;
+    if (a.direct) return 0;
     a.splits = parts;                                         // what the merge kernel adds up
     if (parts * (mix ? H : 1) >= 64) merge_threads = (1024 / Dv) * Dv;               // many pairs to add: more groups share them
     const int groups = merge_threads / Dv;
