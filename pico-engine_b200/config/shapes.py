@@ -111,14 +111,14 @@ def tenusun_shape(width: int, heads: int, kv_heads: int, dim: int, ff: int, laye
                   experts: int = 8, top: int = 2, groups=(4, 2), vdim: int | None = None) -> dict:
     """A Tenusun config.json whose layers take these two forms in turn: latent attention behind a sliding window (a cached row of at
     most 256 entries: rank 2 dim or 256 - dim / 2, rotated part dim / 2, a query row a quarter of the width) with the dense clamped
-    feed-forward, and grouped attention (half of a head rotated, stretched eightfold; values blended from the second such layer on)
+    feed-forward, and grouped attention (half of a head rotated, stretched fourfold; values blended from the second such layer on)
     with a mixture whose experts are a quarter as wide as the dense feed-forward."""
     rot = max(2, dim // 2)
     rank = min(2 * dim, 256 - rot)
     lat = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "kv_rank": rank, "q_rank": max(64, width // 4 // 64 * 64),
-           "scale": (dim + rot) ** -0.5, "rot": {"base": 250000.0, "dims": rot}, "mask": {"size": window}}
+           "scale": (dim + rot) ** -0.5, "rot": {"base": 500000.0, "dims": rot}, "mask": {"size": window}}
     att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim or dim, "scale": dim ** -0.5, "v_mix": True,
-           "rot": {"base": 250000.0, "dims": rot, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+           "rot": {"base": 500000.0, "dims": rot, "scaling": {"factor": 4.0, "original": 8192, "fast": 16.0, "slow": 2.0}}}
     dense = {"kind": "dense", "ff": ff, "limit": 7.0}
     moe = {"kind": "moe", "router": {"experts": experts, "top": top, "groups": {"count": groups[0], "keep": groups[1]}}, "expert": {"ff": ff // 4}}
     out = [{"type": "latent_attention", "mixer": dict(lat), "mlp": dict(dense)} if i % 2 == 0 else

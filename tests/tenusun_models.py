@@ -79,10 +79,10 @@ CONFIGS = {
     # sizes of the tensor-core kernels: head size 64 with 8 query heads on one key/value head and equal values, a window above
     # two pages, latent rows of 64 + 32, query rows wider than key rows; a blending layer behind a latent one; 2 groups of 4, 1 stays
     "T4": config(200, 128, 1e-5, 8.0, [
-        layer(latent(4, 32, 32, 32, 64, 96, 0.125, 40000.0, window=130), moe(8, 2, 32, (2, 1))),
-        layer(attention(8, 1, 64, 64, 0.125, 32, 40000.0, (8.0, 128, 16.0, 1.0), v_mix=True), dense(160, 1.5)),
+        layer(latent(4, 32, 32, 32, 64, 96, 0.11, 40000.0, window=130), moe(8, 2, 32, (2, 1))),
+        layer(attention(8, 1, 64, 64, 0.125, 32, 40000.0, (8.0, 128, 16.0, 1.0), v_mix=True), dense(160, 1.25)),
         layer(attention(8, 1, 64, 64, 0.125, 32, 40000.0, (8.0, 128, 16.0, 1.0), v_mix=True), moe(8, 2, 32, (2, 1))),
-        layer(latent(4, 32, 32, 32, 64, 96, 0.125, 40000.0, window=40), dense(160, 1.5))]),
+        layer(latent(4, 32, 32, 32, 64, 96, 0.11, 40000.0, window=45), dense(160, 1.25))]),
 }
 
 

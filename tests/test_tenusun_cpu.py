@@ -92,12 +92,12 @@ def test_latent_pages_leave_with_the_window_and_the_others_stay():
     model = architecture("Tenusun").build_model(config_from_dict(CONFIGS["T4"]), torch.float32, "meta")
     cache = Cache(model.cache_needs(), 64 * 12, 2, torch.float32, "cpu", allocate=False)
     windows = {g.need.window: g for g in cache.groups}
-    assert set(windows) == {130, 40, None}
+    assert set(windows) == {130, 45, None}
     s = cache.open()
     cache.reserve(s, 500); cache.advance(s, 500)
-    # the next query stands at 500: a window of 130 begins at 371 (page 5), one of 40 at 461 (page 7)
+    # the next query stands at 500: a window of 130 begins at 371 (page 5), one of 45 at 456 (page 7)
     assert [p >= 0 for p in windows[130].table[s]] == [False] * 5 + [True] * 3
-    assert [p >= 0 for p in windows[40].table[s]] == [False] * 7 + [True]
+    assert [p >= 0 for p in windows[45].table[s]] == [False] * 7 + [True]
     assert all(p >= 0 for p in windows[None].table[s])
     cache.check()
     cache.close(s)
