@@ -337,8 +337,6 @@ def tenusun_kernel_times(eng, size: str, tokens: int, batch: int, context: int, 
     entry("prefill latent norm + rotation + cache write + query rows", device_us(lambda: kernels.latent_prepare(
         proj, H, sl.head_dim, R, rank, q_w, lat.dkv_norm, sl.norm_eps, lat.freq, sl.position.dims, q_abs, ctx.tok_pos, ctx.tok_row, kl.k,
         kl.table, kl.stride, halves=True, q_rows=q_rows)), nbytes=tokens * 2 * (H * (rank + R) * 2 + H * R + 2 * (rank + R)))
-    o = torch.randn(H, tokens, sl.v_head_dim, device="cuda").to(bf)
-    entry("prefill heads out of head-major rows", device_us(lambda: kernels.head_gate(o, None, 0)), nbytes=tokens * H * sl.v_head_dim * 2 * 2)
     x = torch.randn(tokens, W, device="cuda")
     y = torch.randn(tokens, W, device="cuda")
     n1, n2 = layers[e_lat].mixer_out_norm, layers[e_lat].feed_forward_norm

@@ -113,8 +113,12 @@ class LatentAttention(Mixer):
                                    halves=isinstance(s.position, RotaryHalvesSpec), q_rows=q_rows)
         a = kernels.attention_headmix(q, q.shape[1], H, 1, rank + R, rank, kv.k, None, kv.table, kv.stride, ctx.tok_pos, ctx.tok_row,
                                       s.window, s.scale, None, None, ctx, values_in_keys=True)
+        if s.gate is None:                                 # no gate: the batched product writes token-major rows itself
+            out = torch.empty(T, H * s.v_head_dim, dtype=a.dtype, device=a.device)
+            torch.bmm(a.view(T, H, rank).transpose(0, 1), self.w_uv, out=out.view(T, H, s.v_head_dim).transpose(0, 1))
+            return out
         o = torch.bmm(a.view(T, H, rank).transpose(0, 1), self.w_uv)                        # [H, T, Dv]
-        return kernels.head_gate(o, proj if s.gate is not None else None, q_w + dkv_w)
+        return kernels.head_gate(o, proj, q_w + dkv_w)
 
     def apply(self, h, ctx, entry, cache_entry, owns_cache, out_dtype=None):
         return linear(self.gated_heads(h, ctx, cache_entry, owns_cache), self.w_o, out_dtype=out_dtype or ctx.dtype)
