@@ -235,6 +235,85 @@ __global__ void __launch_bounds__(256) rotary_half_store_kernel(T* qkv, int ld, 
     }
 }
 
+// bfloat16 with even D, Dv, ld and rot_dims / 2: a lane takes whole pairs of neighbours (4-byte accesses); the partners of a lane's
+// two entries are the two neighbours half the rotated entries away.
+template <int NP>
+__global__ void __launch_bounds__(256) rotary_half_store_pairs_kernel(bf16* qkv, int ld, int H, int G, int D, int Dv, const float* freq, int rot_dims,
+                                                                      float magnitude, int norm, float eps, const int* tok_pos, const int* tok_row,
+                                                                      bf16* k_pool, bf16* v_pool, const int* table, int table_stride, int store,
+                                                                      const bf16* blend, int blend_ld, const void* lambda, int lambda_dtype) {
+    pdl_launch_dependents();
+    __shared__ float s_cos[128], s_sin[128];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    pdl_wait();
+    bf16* row = qkv + (size_t)t * ld;
+    const int pos = tok_pos[t];
+    const int half = rot_dims / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * freq[i], &sn, &cs);
+        s_sin[i] = sn * magnitude; s_cos[i] = cs * magnitude;
+    }
+    long long page = -1;
+    if (store) page = table[(size_t)tok_row[t] * table_stride + pos / PE_PAGE];
+    const float lam = blend ? load_as_f(lambda, lambda_dtype, 0) : 0.f;
+    __syncthreads();
+    const int pairs = D / 2;
+    for (int u = warp; u < H + 2 * G; u += (int)(blockDim.x >> 5)) {
+        if (u < H + G) {
+            __nv_bfloat162* v = reinterpret_cast<__nv_bfloat162*>(row + (size_t)u * D);
+            float2 val[NP];
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < NP; ++e) {
+                const int i = lane + 32 * e, d = 2 * i;
+                float2 f = make_float2(0.f, 0.f);
+                if (i < pairs) {
+                    f = __bfloat1622float2(v[i]);
+                    if (d < rot_dims) {
+                        const bool low = d < half;
+                        const int a = low ? d : d - half;                  // the angle's index of the first of the two entries
+                        const float2 o = __bfloat1622float2(v[low ? i + half / 2 : i - half / 2]);
+                        f = low ? make_float2(fmaf(f.x, s_cos[a], -o.x * s_sin[a]), fmaf(f.y, s_cos[a + 1], -o.y * s_sin[a + 1]))
+                                : make_float2(fmaf(f.x, s_cos[a], o.x * s_sin[a]), fmaf(f.y, s_cos[a + 1], o.y * s_sin[a + 1]));
+                    }
+                }
+                val[e] = f;
+                ss += f.x * f.x + f.y * f.y;
+            }
+            const float rstd = norm ? 1.0f / sqrtf(warp_sum(ss) / (float)D + eps) : 1.0f;
+            __syncwarp();                                                  // every lane has read its partners
+            __nv_bfloat162* dst = (u >= H && store && page >= 0)
+                ? reinterpret_cast<__nv_bfloat162*>(k_pool + (((size_t)page * G + (u - H)) * PE_PAGE + pos % PE_PAGE) * D) : nullptr;
+#pragma unroll
+            for (int e = 0; e < NP; ++e) {
+                const int i = lane + 32 * e;
+                if (i < pairs) {
+                    const __nv_bfloat162 o = __floats2bfloat162_rn(val[e].x * rstd, val[e].y * rstd);
+                    v[i] = o;
+                    if (dst) dst[i] = o;
+                }
+            }
+        } else {
+            const int c = u - H - G;
+            __nv_bfloat162* v = reinterpret_cast<__nv_bfloat162*>(row + (size_t)(H + G) * D + (size_t)c * Dv);
+            __nv_bfloat162* dst = (store && page >= 0)
+                ? reinterpret_cast<__nv_bfloat162*>(v_pool + (((size_t)page * G + c) * PE_PAGE + pos % PE_PAGE) * Dv) : nullptr;
+            const __nv_bfloat162* other = blend ? reinterpret_cast<const __nv_bfloat162*>(blend + (size_t)t * blend_ld + (size_t)c * Dv) : nullptr;
+            if (!other && !dst) continue;
+            for (int d = lane; d < Dv / 2; d += 32) {
+                __nv_bfloat162 o = v[d];
+                if (other) {
+                    const float2 a = __bfloat1622float2(o), b = __bfloat1622float2(other[d]);
+                    o = __floats2bfloat162_rn(fmaf(lam, b.x, (1.0f - lam) * a.x), fmaf(lam, b.y, (1.0f - lam) * a.y));
+                    v[d] = o;
+                }
+                if (dst) dst[d] = o;
+            }
+        }
+    }
+}
+
 extern "C" int pe_rotary_half_store(void* qkv, int dtype, int ld, int T, int H, int G, int D, int Dv, const float* freq, int rot_dims,
                                     float magnitude, int norm, float eps, const int* tok_pos, const int* tok_row, void* k_pool, void* v_pool,
                                     const int* table, int table_stride, int store, const void* blend, int blend_ld, const void* lambda,
@@ -244,6 +323,16 @@ extern "C" int pe_rotary_half_store(void* qkv, int dtype, int ld, int T, int H, 
         return PE_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = H + 2 * G > 16 ? 256 : 128;
+    if (dtype == PE_BF16 && D % 2 == 0 && Dv % 2 == 0 && ld % 2 == 0 && (rot_dims / 2) % 2 == 0 && blend_ld % 2 == 0 &&
+        !(((uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)blend) & 3)) {
+#define ROTH_PAIRS(NP) PE_TRY(pe_launch(rotary_half_store_pairs_kernel<NP>, T, threads, 0, s, (bf16*)qkv, ld, H, G, D, Dv, freq, rot_dims, magnitude, norm, \
+                                        eps, tok_pos, tok_row, (bf16*)k_pool, (bf16*)v_pool, table, table_stride, store, (const bf16*)blend, blend_ld,  \
+                                        lambda, lambda_dtype))
+        if (D <= 64) ROTH_PAIRS(1); else if (D <= 128) ROTH_PAIRS(2); else ROTH_PAIRS(4);
+#undef ROTH_PAIRS
+        PE_LAUNCH_CHECK();
+        return 0;
+    }
 #define ROTH_LAUNCH(TT, NE) PE_TRY(pe_launch(rotary_half_store_kernel<TT, NE>, T, threads, 0, s, (TT*)qkv, ld, H, G, D, Dv, freq, rot_dims, magnitude, \
                                              norm, eps, tok_pos, tok_row, (TT*)k_pool, (TT*)v_pool, table, table_stride, store, (const TT*)blend,      \
                                              blend_ld, lambda, lambda_dtype))
@@ -387,6 +476,26 @@ static int gated_norm_launch(const void* in, int T, int C, int group, const void
     return 0;
 }
 
+// bfloat16 rows times act(gate) without a norm: out[t, c] = in[t, c] * act(gate[t, g_off + c]); eight columns a thread.
+__global__ void gate_mul_bf16x8_kernel(const bf16* in, int C8, const bf16* gate, int g_ld, int g_off, int act, bf16* out, size_t units) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < units; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / C8, c = (idx % C8) * 8;
+        const uint4 a = *reinterpret_cast<const uint4*>(in + idx * 8), g = *reinterpret_cast<const uint4*>(gate + t * g_ld + g_off + c);
+        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+        uint4 o;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 af = __bfloat1622float2(a2[e]), gf = __bfloat1622float2(g2[e]);
+            o2[e] = __floats2bfloat162_rn(af.x * go_act(gf.x, act), af.y * go_act(gf.y, act));
+        }
+        *reinterpret_cast<uint4*>(out + idx * 8) = o;
+    }
+}
+
 extern "C" int pe_gated_norm(const void* in, int in_dtype, int T, int C, int group, const void* weight, int w_dtype, float eps,
                              const void* gate, int g_ld, int g_off, int gate_act, void* out, int out_dtype, void* stream) {
     if (T <= 0 || C <= 0) return 0;
@@ -408,6 +517,15 @@ extern "C" int pe_gated_norm(const void* in, int in_dtype, int T, int C, int gro
     }
     if (in_dtype == PE_F32 && out_dtype == PE_BF16)
         return gated_norm_launch<float, bf16>(in, T, C, group, weight, w_dtype, eps, gate, g_ld, g_off, gate_act, out, s);
+    if (in_dtype == PE_BF16 && out_dtype == PE_BF16 && group == 0 && gate && C % 8 == 0 && g_ld % 8 == 0 && g_off % 8 == 0 &&
+        !(((uintptr_t)in | (uintptr_t)out | (uintptr_t)gate) & 15)) {
+        // no norm, only the gate: eight columns a thread with 16-byte accesses
+        const size_t units = (size_t)T * (C / 8);
+        const int blocks = (int)((units + 255) / 256 < 148 * 16 ? (units + 255) / 256 : 148 * 16);
+        PE_TRY(pe_launch(gate_mul_bf16x8_kernel, blocks, 256, 0, s, (const bf16*)in, C / 8, (const bf16*)gate, g_ld, g_off, gate_act, (bf16*)out, units));
+        PE_LAUNCH_CHECK();
+        return 0;
+    }
     if (in_dtype == PE_BF16 && out_dtype == PE_BF16)
         return gated_norm_launch<bf16, bf16>(in, T, C, group, weight, w_dtype, eps, gate, g_ld, g_off, gate_act, out, s);
     return PE_ERR_UNSUPPORTED;

@@ -343,9 +343,11 @@ def test_window_edges_over_latent_rows_in_prompt_and_decoding(dtype, H, rank, R,
 @pytest.mark.parametrize("H,G,D,Dv,dims,scaling,blend", [(6, 2, 32, 16, 16, (4.0, 64, 8.0, 2.0), True), (3, 1, 24, 12, 10, (8.0, 32, 4.0, 0.5), False),
                                                          (4, 4, 16, 24, 16, None, True), (2, 2, 16, 16, 0, None, True), (4, 2, 128, 32, 48, (6.0, 2048, 24.0, 1.5), True),
                                                          (2, 1, 200, 8, 200, (2.0, 16, 64.0, 32.0), False)])
-def test_rotation_of_halves_with_blended_values_kernel(dtype, H, G, D, Dv, dims, scaling, blend):
+@pytest.mark.parametrize("shift", [1, 2])
+def test_rotation_of_halves_with_blended_values_kernel(dtype, H, G, D, Dv, dims, scaling, blend, shift):
     """Against the plain rotation at positions up to 5000 on rows that carry more columns than q, k and v; the keys and values
-    land at the tokens' places of their pages; blended values are rewritten in the rows and cached; the other columns stay."""
+    land at the tokens' places of their pages; blended values are rewritten in the rows and cached; the other columns stay.  The
+    rows the values are blended with begin ``shift`` entries into wider rows (an odd shift keeps the kernel off its 4-byte path)."""
     from pico_engine.config import RotaryHalvesSpec
     from pico_engine.ops import kernels
     from pico_engine.parts.attention_gated import halves_frequencies
@@ -354,7 +356,7 @@ def test_rotation_of_halves_with_blended_values_kernel(dtype, H, G, D, Dv, dims,
     pos = torch.tensor([0, 1, 2, 63, 64, 65, 700, 4999], dtype=torch.int32)
     T, extra = len(pos), 5
     rows = torch.randn(T, (H + G) * D + G * Dv + extra, generator=g).to(dt)
-    other = torch.randn(T, G * Dv + 3, generator=g).to(dt)
+    other = torch.randn(T, G * Dv + 4, generator=g).to(dt)
     lam = torch.tensor(0.375, dtype=dt)
     sc = None if scaling is None else dict(zip(("factor", "original", "fast", "slow"), scaling))
     freqs, mag = plain.stretched_frequencies(dims, 1000.0, sc)
@@ -365,13 +367,13 @@ def test_rotation_of_halves_with_blended_values_kernel(dtype, H, G, D, Dv, dims,
     table = torch.arange(1, pages + 1, dtype=torch.int32).view(1, -1).cuda()
     dev, odev = rows.cuda().clone(), other.cuda()
     kernels.rotary_half_store(dev, H, G, D, Dv, freq if dims else None, dims, magnitude, False, 1e-6, pos.cuda(), torch.zeros(T, dtype=torch.int32).cuda(),
-                              kp, vp, table, pages, odev[:, 1:1 + G * Dv] if blend else None, lam.cuda() if blend else None)
+                              kp, vp, table, pages, odev[:, shift:shift + G * Dv] if blend else None, lam.cuda() if blend else None)
     got = dev.float().cpu()
     r64 = rows.double()
     want_qk = torch.stack([plain.rotate_half(r64[t:t + 1, :(H + G) * D].view(1, H + G, D), dims, freqs, mag, first=int(pos[t]))[0] for t in range(T)])
     want_v = r64[:, (H + G) * D:(H + G) * D + G * Dv]
     if blend:
-        want_v = (1 - lam.double()) * want_v + lam.double() * other.double()[:, 1:1 + G * Dv]
+        want_v = (1 - lam.double()) * want_v + lam.double() * other.double()[:, shift:shift + G * Dv]
     tol = 3e-5 if dtype == "float32" else 2e-2
     turn = pos.double().view(T, 1, 1) * 2.5e-7 * 5          # the angle is a float32 product: its rounding grows with the position
     assert ((got[:, :(H + G) * D].double().view(T, H + G, D) - want_qk).abs() < tol * 5 + turn).all()
