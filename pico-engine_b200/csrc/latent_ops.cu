@@ -7,7 +7,7 @@
 //
 // The rotation has two layouts: neighbours (2i, 2i+1), or (`halves`) entry i with entry i + rot_dims / 2.
 // latent_prepare: a block a token.  Norms and stores c, turns and stores k_rot (into the cache page of the token), and builds the
-// token's queries [H][rank + R] from the absorbed plain parts qa [H, T, rank] and the turned rotated parts of q.
+// token's queries [H][rank + R] from the absorbed plain parts qa [H, T, rank] (null: they are in q_out already) and the turned rotated parts of q.
 // head_gate: out[t, h, :] = o[h, t, :] * sigmoid(gate logit of head h) (o comes head-major out of a batched product).
 #include "common.cuh"
 
@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(const T* proj, int 
             if (o) o[R - 1] = src[R - 1];
         }
     }
+    if (!qa) return;                                             // the batched product wrote the carried parts into q_out itself
     for (int e = tid; e < H * rank; e += blockDim.x) {
         const int h = e / rank, i = e % rank;
         q_out[((size_t)t * H + h) * W + i] = qa[((size_t)h * n_tokens + t) * rank + i];

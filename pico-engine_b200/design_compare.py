@@ -258,10 +258,10 @@ def pupidra_kernel_times(eng, size: str, tokens: int, batch: int, context: int, 
         qkv, H, G, D, D, None, 0, True, sa.norm_eps, ctx.tok_pos, ctx.tok_row, kv.k, kv.v, kv.table, kv.stride)), nbytes=tokens * (H + 2 * G) * D * 2 * 2)
     kl = ctx.kv(e_lat)
     proj = torch.randn(tokens, lat.w_in.shape[0], device="cuda").to(bf)
-    q_abs = torch.randn(H, tokens, rank, device="cuda").to(bf)
-    entry("prefill latent norm + rotation + cache write + query rows", device_us(lambda: kernels.latent_prepare(
-        proj, H, sl.head_dim, R, rank, q_w, lat.dkv_norm, sl.norm_eps, lat.freq, sl.position.dims, q_abs, ctx.tok_pos, ctx.tok_row, kl.k,
-        kl.table, kl.stride)), nbytes=tokens * 2 * (H * (rank + R) * 2 + H * R + 2 * (rank + R)))
+    q_out = torch.randn(tokens, H * (rank + R), device="cuda").to(bf)      # (the batched product has written the carried parts there)
+    entry("prefill latent norm + rotation + cache write + rotated query parts", device_us(lambda: kernels.latent_prepare(
+        proj, H, sl.head_dim, R, rank, q_w, lat.dkv_norm, sl.norm_eps, lat.freq, sl.position.dims, None, ctx.tok_pos, ctx.tok_row, kl.k,
+        kl.table, kl.stride, q_out=q_out)), nbytes=tokens * 2 * 2 * (H * R + rank + R))
     o = torch.randn(H, tokens, sl.v_head_dim, device="cuda").to(bf)
     entry("prefill heads x sigmoid gate (head-major in)", device_us(lambda: kernels.head_gate(o, proj, q_w + dkv_w)), nbytes=tokens * H * sl.v_head_dim * 2 * 2)
     state_space_calls(ctx, tokens, 1, "prefill")
@@ -333,10 +333,10 @@ def tenusun_kernel_times(eng, size: str, tokens: int, batch: int, context: int, 
     proj = torch.randn(tokens, lat.w_in.shape[0], device="cuda").to(bf)
     entry("prefill norm of the query row", device_us(lambda: kernels.rmsnorm_cols(proj, 0, sl.q_rank, lat.dq_norm, sl.norm_eps)), nbytes=tokens * sl.q_rank * 2 * 2)
     q_rows = torch.randn(tokens, H * (sl.head_dim + R), device="cuda").to(bf)
-    q_abs = torch.randn(H, tokens, rank, device="cuda").to(bf)
-    entry("prefill latent norm + rotation + cache write + query rows", device_us(lambda: kernels.latent_prepare(
-        proj, H, sl.head_dim, R, rank, q_w, lat.dkv_norm, sl.norm_eps, lat.freq, sl.position.dims, q_abs, ctx.tok_pos, ctx.tok_row, kl.k,
-        kl.table, kl.stride, halves=True, q_rows=q_rows)), nbytes=tokens * 2 * (H * (rank + R) * 2 + H * R + 2 * (rank + R)))
+    q_out = torch.randn(tokens, H * (rank + R), device="cuda").to(bf)      # (the batched product has written the carried parts there)
+    entry("prefill latent norm + rotation + cache write + rotated query parts", device_us(lambda: kernels.latent_prepare(
+        proj, H, sl.head_dim, R, rank, q_w, lat.dkv_norm, sl.norm_eps, lat.freq, sl.position.dims, None, ctx.tok_pos, ctx.tok_row, kl.k,
+        kl.table, kl.stride, halves=True, q_rows=q_rows, q_out=q_out)), nbytes=tokens * 2 * 2 * (H * R + rank + R))
     x = torch.randn(tokens, W, device="cuda")
     y = torch.randn(tokens, W, device="cuda")
     n1, n2 = layers[e_lat].mixer_out_norm, layers[e_lat].feed_forward_norm

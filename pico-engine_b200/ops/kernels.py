@@ -1240,18 +1240,26 @@ def gate_norm(y: torch.Tensor, group: int, proj: torch.Tensor, gate_offset: int,
 # ---------------------------------------------------------------------------- attention over low-rank rows
 
 def latent_prepare(proj: torch.Tensor, n_heads: int, head_dim: int, rot_dim: int, rank: int, dkv_offset: int, norm_weight: torch.Tensor,
-                   eps: float, freq: Optional[torch.Tensor], rot_dims: int, q_absorbed: torch.Tensor, tok_pos: torch.Tensor,
+                   eps: float, freq: Optional[torch.Tensor], rot_dims: int, q_absorbed: Optional[torch.Tensor], tok_pos: torch.Tensor,
                    tok_row: torch.Tensor, k_pool: Optional[torch.Tensor], block_table: Optional[torch.Tensor], table_stride: int,
-                   halves: bool = False, q_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   halves: bool = False, q_rows: Optional[torch.Tensor] = None, q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Queries [T, H * (rank + rot_dim)] = [absorbed plain part | turned rotated part] a head, from ``q_absorbed`` [H, T, rank] and the
     rotated parts of the queries in proj [T, ld] (a head = head_dim plain | rot_dim rotated entries); the row [rmsnorm(first rank
     entries at ``dkv_offset``) * norm_weight | turned last rot_dim entries] goes to the token's place in ``k_pool`` [pages, 1, PAGE,
     rank + rot_dim] (skipped when None).  ``halves``: the rotation pairs entry i with entry i + rot_dims / 2 instead of neighbours.
-    ``q_rows`` [T, H * (head_dim + rot_dim)]: the queries lie there and not at the front of proj's rows."""
+    ``q_rows`` [T, H * (head_dim + rot_dim)]: the queries lie there and not at the front of proj's rows.  ``q_absorbed`` None with ``q_out``
+    [T, H * (rank + rot_dim)] given: the absorbed parts stand in ``q_out`` already (a batched product wrote them there) and only the
+    rotated parts are filled in."""
     from .library import state_space
     T, ld = proj.shape
     H, W = n_heads, rank + rot_dim
-    _need(proj, "proj"); _need(q_absorbed, "q_absorbed", proj.dtype, (H, T, rank)); _need(norm_weight, "norm_weight", None, (rank,))
+    _need(proj, "proj"); _need(norm_weight, "norm_weight", None, (rank,))
+    if q_absorbed is not None:
+        _need(q_absorbed, "q_absorbed", proj.dtype, (H, T, rank))
+    elif q_out is None:
+        raise KernelError("without q_absorbed the queries' rows q_out must be given")
+    if q_out is not None:
+        _need(q_out, "q_out", proj.dtype, (T, H * W))
     if rot_dims:
         _need(freq, "freq", torch.float32, (rot_dims // 2,))
     store = k_pool is not None
@@ -1261,10 +1269,10 @@ def latent_prepare(proj: torch.Tensor, n_heads: int, head_dim: int, rot_dim: int
             raise KernelError(f"the cache pool must be [pages, 1, {PAGE}, {W}], not {tuple(k_pool.shape)}")
     if q_rows is not None:
         _need(q_rows, "q_rows", proj.dtype, (T, H * (head_dim + rot_dim)))
-    q = torch.empty(T, H * W, dtype=proj.dtype, device=proj.device)
+    q = q_out if q_out is not None else torch.empty(T, H * W, dtype=proj.dtype, device=proj.device)
     check(state_space().pe_latent_prepare(proj.data_ptr(), _code(proj, "proj"), ld, T, H, head_dim, rot_dim, rank, dkv_offset,
                                           norm_weight.data_ptr(), _code(norm_weight, "norm_weight"), float(eps), _ptr(freq), rot_dims,
-                                          q_absorbed.data_ptr(), q.data_ptr(), tok_pos.data_ptr(), tok_row.data_ptr(), _ptr(k_pool),
+                                          _ptr(q_absorbed), q.data_ptr(), tok_pos.data_ptr(), tok_row.data_ptr(), _ptr(k_pool),
                                           _ptr(block_table), table_stride, 1 if store else 0, 1 if halves else 0, _ptr(q_rows),
                                           0 if q_rows is None else q_rows.shape[1], stream_ptr()), "latent_prepare")
     return q

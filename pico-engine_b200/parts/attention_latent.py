@@ -107,10 +107,12 @@ class LatentAttention(Mixer):
             q_rows = linear(kernels.rmsnorm_cols(proj, 0, s.q_rank, self.dq_norm, s.norm_eps), self.w_uq, out_dtype=ctx.dtype)
         # the plain parts of the queries, head-major, times W_uk: [H, T, D] x [H, D, rank]
         q_plain = (proj[:, :q_w] if q_rows is None else q_rows).view(T, H, D + R)[:, :, :D].transpose(0, 1)
-        q_latent = torch.bmm(q_plain, self.w_uk)
-        q = kernels.latent_prepare(proj, H, D, R, rank, q_w, self.dkv_norm, s.norm_eps, self.freq, s.position.dims, q_latent,
-                                   ctx.tok_pos, ctx.tok_row, kv.k if owns_cache else None, kv.table if owns_cache else None, kv.stride,
-                                   halves=isinstance(s.position, RotaryHalvesSpec), q_rows=q_rows)
+        # (the batched product writes a head's carried part straight into its place of the token's query row)
+        q = torch.empty(T, H * (rank + R), dtype=proj.dtype, device=proj.device)
+        torch.bmm(q_plain, self.w_uk, out=q.view(T, H, rank + R)[:, :, :rank].transpose(0, 1))
+        kernels.latent_prepare(proj, H, D, R, rank, q_w, self.dkv_norm, s.norm_eps, self.freq, s.position.dims, None,
+                               ctx.tok_pos, ctx.tok_row, kv.k if owns_cache else None, kv.table if owns_cache else None, kv.stride,
+                               halves=isinstance(s.position, RotaryHalvesSpec), q_rows=q_rows, q_out=q)
         a = kernels.attention_headmix(q, q.shape[1], H, 1, rank + R, rank, kv.k, None, kv.table, kv.stride, ctx.tok_pos, ctx.tok_row,
                                       s.window, s.scale, None, None, ctx, values_in_keys=True)
         if s.gate is None:                                 # no gate: the batched product writes token-major rows itself
